@@ -1,0 +1,99 @@
+"""Generate the golden vectors under tests/golden/ from the reference's own code.
+
+Run once, in a container that has the reference checkout (it is not needed at
+test time):  python tests/golden/make_golden.py [/path/to/reference]
+
+The reference package cannot be imported as a package (its __init__ pulls in
+cupy), so the two files on the path are loaded by file path:
+  deltazip/core/quant.py          Quantizer.find_params, quantize
+  deltazip/nn_modules/qlinear.py  QuantLinear.pack / unpack / forward
+Everything runs on CPU with torch.  The 2:4 mask is the reference's rule
+(deltazip/core/sparsegpt.py:123-125: per row and per 4 consecutive columns,
+torch.topk(..., 2, largest=False) of w^2 / diag(Hinv)^2 marks the pruned pair)
+with Hinv = I.
+
+Each case is stored as one .npz holding inputs and the reference's outputs.
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _load(path, name):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def reference_case(quant, qlinear, n, k, bits, m, seed, zero_row=False):
+    g = torch.Generator().manual_seed(seed)
+    delta = torch.randn(n, k, generator=g, dtype=torch.float32) * 1e-3
+    if zero_row:
+        delta[1, :] = 0.0          # exercises the all-zero-row branch of find_params
+        delta[2, :] = delta[2, :].abs()  # a row with no negative entry
+    x = torch.randn(m, k, generator=g, dtype=torch.float32).half()
+    w_base = (torch.randn(n, k, generator=g, dtype=torch.float32) * 0.02).half()
+
+    quantizer = quant.Quantizer()
+    quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+    quantizer.find_params(delta, weight=True)
+    scale = quantizer.scale.clone()          # [N, 1]
+    zero = quantizer.zero.clone()            # [N, 1]
+
+    # 2:4 mask, the reference's rule with Hinv = I
+    pruned = torch.zeros_like(delta, dtype=torch.bool)
+    for i in range(0, k, 4):
+        tmp = delta[:, i:i + 4] ** 2
+        pruned.scatter_(1, i + torch.topk(tmp, 2, dim=1, largest=False)[1], True)
+    q_in = delta.clone()
+    q_in[pruned] = 0
+    wq = quant.quantize(q_in, scale, zero, quantizer.maxq)
+
+    layer = qlinear.QuantLinear(bits, k, n, bias=False)
+    lin = torch.nn.Linear(k, n, bias=False)
+    lin.weight.data = wq.clone()
+    layer.pack(lin, scale.clone(), zero.clone(), g_idx=None)
+    dense = layer.unpack().weight.data            # [N, K] float32 holding fp16 values
+    y_delta = layer.forward(x)                    # fp16 [M, N]
+    y_base = torch.nn.functional.linear(x, w_base)  # fp16
+    return dict(
+        bits=np.int32(bits),
+        delta=delta.numpy(), x=x.numpy(), w_base=w_base.numpy(),
+        scale=scale.flatten().numpy(), zero=zero.flatten().numpy(),
+        keep=(~pruned).numpy(), wq=wq.numpy(),
+        qweight=layer.qweight.numpy(), qzeros=layer.qzeros.numpy(),
+        scales=layer.scales.numpy(), g_idx=layer.g_idx.numpy(),
+        dense=dense.half().numpy(),
+        dense_is_fp16_exact=np.bool_(bool((dense.half().float() == dense).all())),
+        y_delta=y_delta.numpy(), y_base=y_base.numpy(),
+    )
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    quant = _load(os.path.join(ref, "deltazip/core/quant.py"), "ref_quant")
+    qlinear = _load(os.path.join(ref, "deltazip/nn_modules/qlinear.py"), "ref_qlinear")
+    torch.set_num_threads(8)
+    cases = [
+        # name, N, K, bits, M, seed, zero_row
+        ("b4_n128_k256", 128, 256, 4, 8, 0, False),
+        ("b2_n128_k256", 128, 256, 2, 8, 1, False),
+        ("b4_n256_k192_edge", 256, 192, 4, 5, 2, True),
+        ("b2_n256_k320_edge", 256, 320, 2, 3, 3, True),
+        ("b8_n64_k128", 64, 128, 8, 4, 4, False),
+    ]
+    for name, n, k, bits, m, seed, zr in cases:
+        out = reference_case(quant, qlinear, n, k, bits, m, seed, zr)
+        assert bool(out["dense_is_fp16_exact"])
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+        print(name, {kk: getattr(v, "shape", None) for kk, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()

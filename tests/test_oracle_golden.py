@@ -1,0 +1,82 @@
+"""Pins the CPU oracle to outputs of the reference's own code (tests/golden/*.npz,
+produced by tests/golden/make_golden.py from deltazip/core/quant.py and
+deltazip/nn_modules/qlinear.py run on CPU)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import deltazip_oracle as O
+
+CASES = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+
+
+@pytest.fixture(params=CASES, ids=[os.path.basename(c)[:-4] for c in CASES])
+def case(request):
+    return dict(np.load(request.param))
+
+
+def test_have_cases():
+    assert len(CASES) >= 5
+
+
+def test_grid_matches_reference(case):
+    bits = int(case["bits"])
+    scale, zero, maxq = O.find_params_sym(case["delta"], bits)
+    np.testing.assert_array_equal(scale, case["scale"])
+    np.testing.assert_array_equal(zero, case["zero"])
+    assert maxq == 2 ** bits - 1
+
+
+def test_mask_matches_reference(case):
+    np.testing.assert_array_equal(O.mask_2_4(case["delta"]), case["keep"])
+
+
+def test_quantised_values_match_reference(case):
+    bits = int(case["bits"])
+    wq, scale, zero = O.compress_delta(case["delta"], bits)
+    np.testing.assert_array_equal(wq, case["wq"])
+
+
+def test_pack_bit_exact(case):
+    bits = int(case["bits"])
+    qw, qz, sc = O.pack(case["wq"], case["scale"], case["zero"], bits)
+    np.testing.assert_array_equal(qw, case["qweight"])
+    np.testing.assert_array_equal(qz, case["qzeros"])
+    np.testing.assert_array_equal(sc.view(np.uint16), case["scales"].view(np.uint16))
+
+
+def test_unpack_bit_exact(case):
+    bits = int(case["bits"])
+    d = O.unpack(case["qweight"], case["qzeros"], case["scales"], bits)
+    assert d.dtype == np.float16
+    np.testing.assert_array_equal(d.view(np.uint16), case["dense"].view(np.uint16))
+
+
+def test_forward_close_to_reference(case):
+    bits = int(case["bits"])
+    y = O.delta_forward(case["x"], case["qweight"], case["qzeros"], case["scales"], bits)
+    # same fp16 operands; only the accumulation order inside the BLAS differs
+    assert O.rel_l2(y, case["y_delta"]) <= 2e-3
+    yb = O.base_linear(case["x"], case["w_base"])
+    assert O.rel_l2(yb, case["y_base"]) <= 2e-3
+
+
+def test_sparsity_is_2_4(case):
+    bits = int(case["bits"])
+    q, z = O.unpack_codes(case["qweight"], case["qzeros"], bits)
+    nz = (q != z[None, :]).T  # [N, K]
+    n, k = nz.shape
+    assert nz.reshape(n, k // 4, 4).sum(axis=2).max() <= 2
+
+
+def test_apply_delta_semantics():
+    w, deltas = O.make_layer(128, 128, 3, 4, seed=5)
+    x, idx = O.make_tokens(11, 128, 3, seed=5, base_frac=0.3)
+    y = O.apply_delta(x, w, deltas, idx)
+    for i in range(11):
+        yi = O.base_linear(x[i:i + 1], w)
+        if idx[i] >= 0:
+            yi = (yi + O.delta_forward(x[i:i + 1], *deltas[idx[i]])).astype(np.float16)
+        np.testing.assert_array_equal(y[i:i + 1].view(np.uint16), yi.view(np.uint16))
