@@ -1,0 +1,230 @@
+"""Tensor-level operators over the C ABI.
+
+`apply_delta` keeps the signature of the reference's op
+(serving/vllm/delta/deltazip_marlin.py:10-19):
+
+    y = apply_delta(x, qweight_stacked, scales_stacked, meta_stacked, indices, base_weight)
+
+All tensors are CUDA tensors; work is enqueued on torch's current stream.
+PyTorch is used for memory and streams only -- every computation below runs in
+libdeltazip_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import SbmmArgs, check, lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("deltazip_b200 operators take CUDA tensors only (no CPU path)")
+
+
+# ---------------------------------------------------------------------------
+# slot format
+# ---------------------------------------------------------------------------
+
+def slot_shapes(n: int, k: int, bits: int) -> Tuple[Tuple[int, int], Tuple[int, int], Tuple[int, int]]:
+    """(qweight int32, meta int16, scales fp16) shapes of one slot of a [n, k] layer.
+
+    Same outer shapes as the reference's stacked tensors
+    (serving/vllm/delta/layers_marlin.py:311-333) for 4-bit; for 2-bit the
+    metadata keeps k/16 int16 per row (the reference formula would give k/32,
+    which cannot hold two 2-bit positions per group of four)."""
+    return (k * bits // 128, 2 * n), (n, k // 16), (1, n)
+
+
+def alloc_slots(num_slots: int, n: int, k: int, bits: int, device) -> Tuple[torch.Tensor, ...]:
+    qs, ms, ss = slot_shapes(n, k, bits)
+    return (torch.zeros((num_slots, *qs), dtype=torch.int32, device=device),
+            torch.zeros((num_slots, *ms), dtype=torch.int16, device=device),
+            torch.zeros((num_slots, *ss), dtype=torch.float16, device=device))
+
+
+def convert_from_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, bits: int,
+                      out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+                      check_status: bool = True):
+    """GPTQ-layout tensors of one delta layer -> (qweight, meta, scales) in slot layout."""
+    _need_cuda(qweight, qzeros, scales)
+    k = qweight.shape[0] * 32 // bits
+    n = qweight.shape[1]
+    qweight = qweight.contiguous()
+    qzeros = qzeros.contiguous()
+    scales = scales.contiguous()
+    if out is None:
+        qs, ms, ss = slot_shapes(n, k, bits)
+        out = (torch.empty(qs, dtype=torch.int32, device=qweight.device),
+               torch.empty(ms, dtype=torch.int16, device=qweight.device),
+               torch.empty(ss, dtype=torch.float16, device=qweight.device))
+    sq, sm, ss_ = out
+    status = torch.zeros(1, dtype=torch.int32, device=qweight.device)
+    check(lib().dz_convert_from_gptq(qweight.data_ptr(), qzeros.data_ptr(), scales.data_ptr(),
+                                     n, k, bits, sq.data_ptr(), sm.data_ptr(), ss_.data_ptr(),
+                                     status.data_ptr(), _stream()), "dz_convert_from_gptq")
+    if check_status:
+        host = ctypes.c_int(0)
+        check(lib().dz_read_status(status.data_ptr(), _stream(), ctypes.byref(host)), "dz_read_status")
+        check(host.value, "dz_convert_from_gptq(device)")
+    return out
+
+
+def unpack(slot_qweight: torch.Tensor, slot_meta: torch.Tensor, slot_scales: torch.Tensor,
+           n: int, k: int, bits: int) -> torch.Tensor:
+    """Dense fp16 delta [n, k] of one slot (bit-identical to QuantLinear.unpack)."""
+    _need_cuda(slot_qweight, slot_meta, slot_scales)
+    out = torch.empty((n, k), dtype=torch.float16, device=slot_qweight.device)
+    check(lib().dz_unpack(slot_qweight.data_ptr(), slot_meta.data_ptr(), slot_scales.data_ptr(),
+                          n, k, bits, out.data_ptr(), _stream()), "dz_unpack")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# batch metadata
+# ---------------------------------------------------------------------------
+
+class Segments:
+    """Device-side segment table for one batch (one scheduling step).
+
+    Built from the per-token slot indices (`base_indices` of the reference's
+    convert_mapping, serving/vllm/delta/models.py:69-145) and shared by every
+    layer of the step."""
+
+    def __init__(self, max_tokens: int, num_slots: int, device):
+        self.max_tokens = int(max_tokens)
+        self.num_slots = int(num_slots)
+        nbytes = lib().dz_segments_bytes(self.max_tokens, self.num_slots)
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        self.m = 0
+        self._key = None
+
+    def build(self, indices: torch.Tensor) -> "Segments":
+        _need_cuda(indices)
+        m = indices.numel()
+        if m > self.max_tokens:
+            raise ValueError(f"{m} tokens exceed the table capacity {self.max_tokens}")
+        if indices.dtype == torch.int64:
+            dt = _lib.DZ_INDEX_I64
+        elif indices.dtype == torch.int32:
+            dt = _lib.DZ_INDEX_I32
+        else:
+            raise ValueError("indices must be int32 or int64")
+        indices = indices.contiguous()
+        check(lib().dz_build_segments(indices.data_ptr(), dt, m, self.num_slots,
+                                      self.buf.data_ptr(), _stream()), "dz_build_segments")
+        self.m = m
+        return self
+
+    def header(self):
+        """(M, num_slots, num_token_blocks, sorted, status, num_windows, num_active) -- syncs."""
+        return tuple(self.buf[:32].view(torch.int32)[:7].tolist())
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """One grow-only scratch buffer per (device, stream).  The SBMM kernel keeps
+    split-K partial tiles and tile counters here; calls on one stream are
+    ordered, so they can share it."""
+    key = (device.index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return _lib.DZ_DTYPE_F16
+    if t.dtype == torch.bfloat16:
+        return _lib.DZ_DTYPE_BF16
+    raise ValueError(f"unsupported activation dtype {t.dtype}")
+
+
+def _bits_from_shapes(qweight_stacked: torch.Tensor, k: int) -> int:
+    # qweight slot is [k * bits / 128, 2n] int32
+    return qweight_stacked.shape[-2] * 128 // k
+
+
+def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
+         meta_stacked: torch.Tensor, segments: Segments, base_weight: torch.Tensor,
+         out: Optional[torch.Tensor] = None, bits: Optional[int] = None,
+         _entry: str = "dz_sbmm") -> torch.Tensor:
+    """y = x W^T + x dequant(delta_slot(i))^T with a prebuilt segment table."""
+    _need_cuda(x, qweight_stacked, scales_stacked, meta_stacked, base_weight)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    n = base_weight.shape[0]
+    if base_weight.shape[1] != k or not base_weight.is_contiguous():
+        raise ValueError("base_weight must be a contiguous [N, K] tensor matching x")
+    if segments.m != m:
+        raise ValueError(f"segment table was built for {segments.m} tokens, x has {m}")
+    if bits is None:
+        bits = _bits_from_shapes(qweight_stacked, k)
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    nbytes = lib().dz_sbmm_workspace_bytes(m, n, k)
+    ws = _workspace(x.device, nbytes)
+    args = SbmmArgs(
+        x=x2.data_ptr(), w_base=base_weight.data_ptr(),
+        qweight=qweight_stacked.data_ptr(), meta=meta_stacked.data_ptr(),
+        scales=scales_stacked.data_ptr(),
+        qweight_stride=qweight_stacked.stride(0) * 4, meta_stride=meta_stacked.stride(0) * 2,
+        scales_stride=scales_stacked.stride(0) * 2,
+        segments=segments.buf.data_ptr(), y=out.data_ptr(),
+        M=m, N=n, K=k, num_slots=qweight_stacked.shape[0], bits=bits, dtype=_dtype_code(x),
+        workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    check(getattr(lib(), _entry)(ctypes.byref(args), _stream()), _entry)
+    return out.reshape(*x.shape[:-1], n)
+
+
+def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x W^T on the same kernel (every token base-only)."""
+    _need_cuda(x, base_weight)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    n = base_weight.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    ws = _workspace(x.device, lib().dz_sbmm_workspace_bytes(m, n, k))
+    args = SbmmArgs(x=x2.data_ptr(), w_base=base_weight.data_ptr(), y=out.data_ptr(),
+                    M=m, N=n, K=k, num_slots=0, bits=4, dtype=_dtype_code(x),
+                    workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    check(lib().dz_base_gemm(ctypes.byref(args), _stream()), "dz_base_gemm")
+    return out.reshape(*x.shape[:-1], n)
+
+
+_segment_cache = {}
+
+
+def apply_delta(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
+                meta_stacked: torch.Tensor, indices: torch.Tensor,
+                base_weight: torch.Tensor) -> torch.Tensor:
+    """Drop-in for the reference op: builds the segment table from `indices`
+    on every call.  Layers that share one mapping per step should build a
+    `Segments` once (set_mapping does) and call `sbmm`."""
+    m = indices.numel()
+    num_slots = qweight_stacked.shape[0]
+    key = (x.device.index, _stream(), num_slots)
+    seg = _segment_cache.get(key)
+    if seg is None or seg.max_tokens < m:
+        seg = Segments(max(m, 256), num_slots, x.device)
+        _segment_cache[key] = seg
+    seg.build(indices)
+    return sbmm(x, qweight_stacked, scales_stacked, meta_stacked, seg, base_weight)

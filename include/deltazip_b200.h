@@ -1,0 +1,152 @@
+/*
+ * deltazip_b200 -- C ABI of the B200-native selective batched matmul (SBMM) path.
+ *
+ * Plain C: pointers and sizes only.  All data pointers are CUDA device pointers
+ * unless a parameter says "host".  `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  Every entry point returns a dz_status
+ * (0 = ok) and never exits, traps or synchronises the device unless it says so.
+ * Nothing here allocates device memory on the hot path: the caller supplies a
+ * workspace of dz_sbmm_workspace_bytes().
+ *
+ * Each declaration cites the piece of the reference (eth-easl/deltazip, paths
+ * relative to its checkout) whose role it takes over.
+ */
+#ifndef DELTAZIP_B200_H_
+#define DELTAZIP_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  DZ_OK = 0,
+  DZ_ERR_INVALID_ARG = 1,   /* null pointer, negative size, bad enum            */
+  DZ_ERR_SHAPE = 2,         /* N % 128 != 0, K % 64 != 0, unsupported bits      */
+  DZ_ERR_ALIGNMENT = 3,     /* pointer / stride not 16-byte aligned             */
+  DZ_ERR_WORKSPACE = 4,     /* workspace too small                              */
+  DZ_ERR_SLOT_RANGE = 5,    /* a delta index >= num_slots                       */
+  DZ_ERR_NOT_2_4 = 6,       /* converter: a group of 4 holds more than 2 codes
+                               different from the zero-point                    */
+  DZ_ERR_NOT_SYMMETRIC = 7, /* converter: a stored zero-point != 2^(bits-1) - 1 */
+  DZ_ERR_CUDA = 8,          /* a CUDA runtime / driver call failed              */
+  DZ_ERR_TIMEOUT = 9,       /* a bounded device-side wait ran out               */
+  DZ_ERR_UNSUPPORTED = 10,  /* valid request this build does not implement      */
+  DZ_ERR_TOO_LARGE = 11     /* size beyond a fixed maximum of the entry point   */
+} dz_status;
+
+enum { DZ_DTYPE_F16 = 0, DZ_DTYPE_BF16 = 1 };
+enum { DZ_INDEX_I32 = 0, DZ_INDEX_I64 = 1 };
+
+/* Library version (major*10000 + minor*100 + patch). */
+int dz_version(void);
+/* Static, human readable text for a dz_status. */
+const char* dz_status_string(int status);
+/* Text of the last CUDA error this thread's calls into the library met ("" if none). */
+const char* dz_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------
+ * Slot format.  One delta of one linear layer [N out, K in] occupies three
+ * device arrays whose names, dtypes and outer shapes are those the reference's
+ * delta layers allocate (serving/vllm/delta/layers_marlin.py:311-333,407-429,
+ * 510-534):
+ *   qweight int32 [K*bits/128, 2N]   codes of the K/2 kept values of every row
+ *   meta    int16 [N, K/16]          2:4 positions (two 2-bit indices / group)
+ *   scales  fp16  [1, N]             per-output-channel scale
+ * The element order inside qweight / meta is this library's own (tile-major,
+ * see dz_convert_from_gptq); the reference's order is that of an external
+ * package whose source it does not ship.
+ * ------------------------------------------------------------------------ */
+size_t dz_slot_qweight_bytes(int N, int K, int bits);
+size_t dz_slot_meta_bytes(int N, int K);
+size_t dz_slot_scales_bytes(int N);
+
+/*
+ * GPTQ layout -> slot layout, on the device.
+ * Takes the tensors deltazip/nn_modules/qlinear.py:83-183 (QuantLinear.pack)
+ * writes: qweight int32 [K*bits/32, N], qzeros int32 [1, N*bits/32], scales
+ * fp16 [1, N]; fills the role of deltazip/utils/converter.py:12-101, which hands
+ * the same tensors to an external packer.  bits in {2, 4}.
+ * `status_word` (device int, may be NULL) receives the first DZ_ERR_NOT_2_4 /
+ * DZ_ERR_NOT_SYMMETRIC found; the call itself is asynchronous.
+ */
+int dz_convert_from_gptq(const int32_t* qweight, const int32_t* qzeros,
+                         const uint16_t* scales, int N, int K, int bits,
+                         void* slot_qweight, void* slot_meta, uint16_t* slot_scales,
+                         int* status_word, void* stream);
+
+/*
+ * Slot layout -> dense delta, fp16 [N, K] row-major; bit-identical to
+ * QuantLinear.unpack (deltazip/nn_modules/qlinear.py:185-264) of the GPTQ
+ * tensors the slot was converted from.
+ */
+int dz_unpack(const void* slot_qweight, const void* slot_meta, const uint16_t* slot_scales,
+              int N, int K, int bits, uint16_t* delta_out, void* stream);
+
+/*
+ * Batch metadata.  Turns the per-token slot ids (`indices`, the `base_indices`
+ * tensor of serving/vllm/delta/models.py:69-145, -1 = base model only) into the
+ * segment table the SBMM kernel walks.  Build once per scheduling step and share
+ * across all layers, as the reference shares its index buffers
+ * (serving/vllm/delta/models.py:407-430).  `segments` must hold
+ * dz_segments_bytes(M_max, num_slots) bytes.  Indices >= num_slots set
+ * DZ_ERR_SLOT_RANGE in the table's status field and are treated as -1.
+ */
+size_t dz_segments_bytes(int M, int num_slots);
+int dz_build_segments(const void* indices, int index_dtype, int M, int num_slots,
+                      void* segments, void* stream);
+
+/*
+ * The hot path:  y[i] = x[i] W^T + x[i] dequant(delta_{indices[i]})^T.
+ * Replaces apply_delta (serving/vllm/delta/deltazip_marlin.py:10-19), i.e. the
+ * external sbmm_4bit_2_4_native(qweight_stacked, x, meta_stacked, scales_stacked,
+ * indices, base_weight), and the separate base GEMM
+ * (serving/vllm/model_executor/layers/linear.py:85-96).
+ */
+typedef struct {
+  const void* x;            /* [M, K] row-major, 16-byte aligned                 */
+  const void* w_base;       /* [N, K] row-major, 16-byte aligned                 */
+  const void* qweight;      /* slot 0 of the qweight stack                       */
+  const void* meta;         /* slot 0 of the meta stack                          */
+  const void* scales;       /* slot 0 of the scales stack                        */
+  int64_t qweight_stride;   /* bytes between consecutive slots                   */
+  int64_t meta_stride;
+  int64_t scales_stride;
+  const void* segments;     /* table from dz_build_segments for this batch       */
+  void* y;                  /* [M, N] row-major                                  */
+  int32_t M, N, K;
+  int32_t num_slots;
+  int32_t bits;             /* 2 or 4 (all slots of a stack share it)            */
+  int32_t dtype;            /* DZ_DTYPE_* of x, w_base and y                     */
+  void* workspace;          /* >= dz_sbmm_workspace_bytes(M, N, K)               */
+  size_t workspace_bytes;
+} dz_sbmm_args;
+
+size_t dz_sbmm_workspace_bytes(int M, int N, int K);
+int dz_sbmm(const dz_sbmm_args* args, void* stream);
+
+/* Base GEMM alone, y = x W^T (all tokens -1); same argument block, the slot
+ * pointers and `segments` may be NULL.
+ * serving/vllm/model_executor/layers/linear.py:85-96 */
+int dz_base_gemm(const dz_sbmm_args* args, void* stream);
+
+/*
+ * Delta swap-in: one asynchronous host->device copy of a delta's slot bytes
+ * from PINNED host memory on `copy_stream`, preceded by a zero fill of the
+ * destination when `zero_first` != 0 (the reference resets a slot before it
+ * overwrites it, serving/vllm/delta/layers_marlin.py:342-360).  Returns without
+ * waiting; record / wait on an event in `copy_stream` to publish the slot.
+ */
+int dz_slot_upload(void* dst_device, const void* src_pinned_host, size_t bytes,
+                   int zero_first, void* copy_stream);
+int dz_slot_reset(void* dst_device, size_t bytes, void* stream);
+
+/* Reads and clears a device status word (synchronises `stream`). */
+int dz_read_status(int* status_word, void* stream, int* host_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DELTAZIP_B200_H_ */
