@@ -40,6 +40,7 @@ class SbmmArgs(Structure):
         ("segments", c_void_p), ("y", c_void_p),
         ("M", c_int32), ("N", c_int32), ("K", c_int32),
         ("num_slots", c_int32), ("bits", c_int32), ("dtype", c_int32),
+        ("tokens_sorted", c_int32), ("reserved", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
     ]
 
@@ -67,7 +68,7 @@ _SIGNATURES = {
     "dz_unpack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dz_segments_bytes": (c_size_t, [c_int, c_int]),
     "dz_build_segments": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "dz_sbmm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "dz_sbmm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "dz_sbmm": (c_int, [POINTER(SbmmArgs), c_void_p]),
     "dz_base_gemm": (c_int, [POINTER(SbmmArgs), c_void_p]),
     "dz_slot_upload": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),

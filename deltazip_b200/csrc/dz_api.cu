@@ -24,6 +24,7 @@ static int check_shape(int N, int K, int bits) {
 static int check_sbmm_args(const dz_sbmm_args* a, bool base_only) {
   if (!a) return DZ_ERR_INVALID_ARG;
   if (a->M < 0) return DZ_ERR_INVALID_ARG;
+  if (a->M == 0) return DZ_OK;  // nothing to do; pointers may be null
   if (!a->x || !a->w_base || !a->y) return DZ_ERR_INVALID_ARG;
   int rc = check_shape(a->N, a->K, base_only ? 4 : a->bits);
   if (rc) return rc;
@@ -37,7 +38,7 @@ static int check_sbmm_args(const dz_sbmm_args* a, bool base_only) {
         (a->meta_stride & 15) || (a->scales_stride & 1))
       return DZ_ERR_ALIGNMENT;
   }
-  if (a->workspace_bytes < sbmm_workspace_bytes(a->M, a->N, a->K)) return DZ_ERR_WORKSPACE;
+  if (a->workspace_bytes < sbmm_workspace_bytes(a->M, a->N, a->K, base_only ? 1 : a->tokens_sorted)) return DZ_ERR_WORKSPACE;
   if (a->workspace_bytes && (!a->workspace || !aligned16(a->workspace))) return DZ_ERR_ALIGNMENT;
   return DZ_OK;
 }
@@ -117,24 +118,26 @@ int dz_build_segments(const void* indices, int index_dtype, int M, int num_slots
   return launch_build_segments(indices, index_dtype, M, num_slots, segments, (cudaStream_t)stream);
 }
 
-size_t dz_sbmm_workspace_bytes(int M, int N, int K) { return sbmm_workspace_bytes(M, N, K); }
+size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted) {
+  return sbmm_workspace_bytes(M, N, K, tokens_sorted);
+}
 
 int dz_sbmm(const dz_sbmm_args* args, void* stream) {
   int rc = check_sbmm_args(args, false);
-  if (rc) return rc;
+  if (rc || args->M == 0) return rc;
   return launch_sbmm(*args, false, (cudaStream_t)stream);
 }
 
 int dz_base_gemm(const dz_sbmm_args* args, void* stream) {
   int rc = check_sbmm_args(args, true);
-  if (rc) return rc;
+  if (rc || args->M == 0) return rc;
   return launch_sbmm(*args, true, (cudaStream_t)stream);
 }
 
 // Validation twin of dz_sbmm on CUDA cores (same arguments, no workspace use).
 int dz_sbmm_simt(const dz_sbmm_args* args, void* stream) {
   int rc = check_sbmm_args(args, false);
-  if (rc) return rc;
+  if (rc || args->M == 0) return rc;
   return launch_sbmm_simt(*args, false, (cudaStream_t)stream);
 }
 

@@ -72,7 +72,7 @@ __host__ __device__ inline size_t meta_offset(int n, int kb, int num_kb, int c, 
 // [lo, hi) zeroed.
 // ---------------------------------------------------------------------------
 constexpr int kTokenBlock = 256;
-constexpr int kMaxWindowCols = 64;
+constexpr int kMaxWindowCols = 32;
 constexpr int kMaxSlots = 4096;
 
 struct SegHeader {
@@ -91,7 +91,7 @@ static_assert(sizeof(SegHeader) == 64, "header is one 64-byte line");
 struct Window {
   int32_t slot;
   int32_t col0;   // first sorted position, multiple of 16
-  int32_t ncols;  // 16, 32, 48 or 64
+  int32_t ncols;  // 16 or 32
   int32_t lo;     // valid sorted positions [lo, hi)
   int32_t hi;
   int32_t pad[3];
@@ -143,7 +143,7 @@ int launch_unpack(const void* sq, const void* sm, const uint16_t* ss, int N, int
                   uint16_t* out, cudaStream_t st);
 int launch_build_segments(const void* indices, int index_dtype, int M, int num_slots,
                           void* segments, cudaStream_t st);
-size_t sbmm_workspace_bytes(int M, int N, int K);
+size_t sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted);
 int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st);
 
 }  // namespace dz

@@ -105,9 +105,12 @@ class Segments:
         nbytes = lib().dz_segments_bytes(self.max_tokens, self.num_slots)
         self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         self.m = 0
-        self._key = None
+        self.sorted = True
 
-    def build(self, indices: torch.Tensor) -> "Segments":
+    def build(self, indices: torch.Tensor, sorted_hint: Optional[bool] = None) -> "Segments":
+        """Builds the table on the current stream.  `sorted_hint` says whether
+        `indices` is non-decreasing (the reference's scheduler delivers batches
+        sorted by delta id); None checks on the device (one host sync)."""
         _need_cuda(indices)
         m = indices.numel()
         if m > self.max_tokens:
@@ -122,6 +125,9 @@ class Segments:
         check(lib().dz_build_segments(indices.data_ptr(), dt, m, self.num_slots,
                                       self.buf.data_ptr(), _stream()), "dz_build_segments")
         self.m = m
+        if sorted_hint is None:
+            sorted_hint = bool(m < 2 or (indices[1:] >= indices[:-1]).all().item())
+        self.sorted = bool(sorted_hint)
         return self
 
     def header(self):
@@ -142,6 +148,19 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def read_status(device=None) -> int:
+    """Reads and clears the status word the SBMM kernel leaves in the current
+    stream's workspace (0 = ok, DZ_ERR_TIMEOUT = a bounded device-side wait ran
+    out, DZ_ERR_INVALID_ARG = a wrong `tokens_sorted` promise).  Synchronises."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspaces.get((device.index, _stream()))
+    if ws is None:
+        return 0
+    host = ctypes.c_int(0)
+    check(lib().dz_read_status(ws.data_ptr(), _stream(), ctypes.byref(host)), "dz_read_status")
+    return host.value
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -176,7 +195,9 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
         bits = _bits_from_shapes(qweight_stacked, k)
     if out is None:
         out = torch.empty((m, n), dtype=x.dtype, device=x.device)
-    nbytes = lib().dz_sbmm_workspace_bytes(m, n, k)
+    if m == 0:
+        return out.reshape(*x.shape[:-1], n)
+    nbytes = lib().dz_sbmm_workspace_bytes(m, n, k, int(segments.sorted))
     ws = _workspace(x.device, nbytes)
     args = SbmmArgs(
         x=x2.data_ptr(), w_base=base_weight.data_ptr(),
@@ -186,6 +207,7 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
         scales_stride=scales_stacked.stride(0) * 2,
         segments=segments.buf.data_ptr(), y=out.data_ptr(),
         M=m, N=n, K=k, num_slots=qweight_stacked.shape[0], bits=bits, dtype=_dtype_code(x),
+        tokens_sorted=int(segments.sorted),
         workspace=ws.data_ptr(), workspace_bytes=ws.numel())
     check(getattr(lib(), _entry)(ctypes.byref(args), _stream()), _entry)
     return out.reshape(*x.shape[:-1], n)
@@ -202,9 +224,11 @@ def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
     n = base_weight.shape[0]
     if out is None:
         out = torch.empty((m, n), dtype=x.dtype, device=x.device)
-    ws = _workspace(x.device, lib().dz_sbmm_workspace_bytes(m, n, k))
+    if m == 0:
+        return out.reshape(*x.shape[:-1], n)
+    ws = _workspace(x.device, lib().dz_sbmm_workspace_bytes(m, n, k, 1))
     args = SbmmArgs(x=x2.data_ptr(), w_base=base_weight.data_ptr(), y=out.data_ptr(),
-                    M=m, N=n, K=k, num_slots=0, bits=4, dtype=_dtype_code(x),
+                    M=m, N=n, K=k, num_slots=0, bits=4, dtype=_dtype_code(x), tokens_sorted=1,
                     workspace=ws.data_ptr(), workspace_bytes=ws.numel())
     check(lib().dz_base_gemm(ctypes.byref(args), _stream()), "dz_base_gemm")
     return out.reshape(*x.shape[:-1], n)

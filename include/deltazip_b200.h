@@ -120,11 +120,21 @@ typedef struct {
   int32_t num_slots;
   int32_t bits;             /* 2 or 4 (all slots of a stack share it)            */
   int32_t dtype;            /* DZ_DTYPE_* of x, w_base and y                     */
-  void* workspace;          /* >= dz_sbmm_workspace_bytes(M, N, K)               */
+  int32_t tokens_sorted;    /* 1: caller guarantees `indices` were non-decreasing
+                               (the reference's scheduler sorts each batch by
+                               delta id, serving/vllm/core/scheduler.py:101-104);
+                               x is then read in place.  0: x is first gathered
+                               into sorted order inside the workspace.  A wrong
+                               promise is detected (DZ_ERR_INVALID_ARG in the
+                               workspace status word) and nothing is computed.  */
+  int32_t reserved;
+  void* workspace;          /* >= dz_sbmm_workspace_bytes(M, N, K, tokens_sorted);
+                               zero-filled once by the caller before first use;
+                               its first int is a status word (dz_read_status)  */
   size_t workspace_bytes;
 } dz_sbmm_args;
 
-size_t dz_sbmm_workspace_bytes(int M, int N, int K);
+size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted);
 int dz_sbmm(const dz_sbmm_args* args, void* stream);
 
 /* Base GEMM alone, y = x W^T (all tokens -1); same argument block, the slot

@@ -44,6 +44,8 @@ def test_host_functions(handle):
     assert L.dz_slot_qweight_bytes(100, 4096, 4) == 0      # N % 128 != 0
     assert L.dz_slot_qweight_bytes(128, 4096, 3) == 0      # 3-bit unsupported
     assert L.dz_segments_bytes(64, 8) > 64
+    assert L.dz_sbmm_workspace_bytes(64, 4096, 4096, 1) > 0
+    assert L.dz_sbmm_workspace_bytes(64, 4096, 4096, 0) > L.dz_sbmm_workspace_bytes(64, 4096, 4096, 1)
     assert b"2:4" in L.dz_status_string(_lib.DZ_ERR_NOT_2_4)
 
 

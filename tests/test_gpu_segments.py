@@ -6,7 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def expected_windows(idx, num_slots, token_block=256, max_cols=64):
+def expected_windows(idx, num_slots, token_block=256, max_cols=32):
     idx = np.where((idx >= num_slots) | (idx < -1), -1, idx)
     order = np.sort(idx, kind="stable")
     wins = []
