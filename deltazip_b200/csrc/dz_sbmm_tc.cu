@@ -22,12 +22,16 @@
 // fragment of a tile to finish (a per-tile counter) adds the partials in fixed
 // order, so results do not depend on timing.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 2-5 = code expansion and epilogue (one TMEM lane each).
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, then four
+// warpgroups of 128 threads that expand codes (delta stage s goes to warpgroup
+// s mod 4, so several stages are expanded at once and each scheduler has four
+// warps to hide latency with) and share the epilogue by column chunks.
 // Every mbarrier wait is bounded: on a timeout the CTA records DZ_ERR_TIMEOUT,
 // raises an abort flag that turns every later wait into a no-op, runs its
 // (bounded) loops to the end and frees its tensor memory.
 #include <cuda.h>
+
+#include <stdlib.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -38,16 +42,17 @@ namespace dz {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kNumWG = 4;                      // code-expansion warpgroups (128 threads each)
+constexpr int kThreads = 64 + 128 * kNumWG;
 constexpr int kUnitK = 128;                    // dense k per work unit
 constexpr int kATile = 128 * 128;              // bytes: 128 rows x 128 B
-constexpr int kNumABuf = 2;                    // expanded-A buffers
-constexpr int kDeltaStages = 6;
+constexpr int kNumABuf = kNumWG;               // expanded-A buffers, one per warpgroup
+constexpr int kDeltaStages = 6;                // upper bound; Params::delta_stages are used
 constexpr int kRawBytes = 4096;                // codes of one unit (4-bit)
 constexpr int kMetaBytes = 2048;               // metadata of one unit
 constexpr int kWinBytes = 2 * kMaxWindowCols * 128;
 constexpr int kDeltaStageBytes = kRawBytes + kMetaBytes + kWinBytes;
-constexpr int kBaseRingBytes = 96 * 1024;
+constexpr int kBaseRingBytes = 72 * 1024;
 constexpr int kMaxWin = 256;                   // windows of one token block
 constexpr int kTmemCols = 512;
 constexpr int kMetaCol = 256;                  // first TMEM column of the metadata buffers
@@ -61,8 +66,9 @@ struct Params {
   int num_kunits, num_tiles, num_kblocks;
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
   int base_only, tokens_sorted;
+  int debug;   // experiment switches (bit 0: skip code expansion, bit 1: skip window zeroing)
   int grid, total_units;
-  int base_stages, xb_bytes;
+  int base_stages, delta_stages, xb_bytes;
   const uint8_t* qweight;
   const uint8_t* meta;
   const uint8_t* scales;
@@ -238,7 +244,8 @@ struct WinS {
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 1)
 sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               const Params p) {
+               const __grid_constant__ CUtensorMap map_x32,
+               const __grid_constant__ CUtensorMap map_xc, const Params p) {
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t s_bars[4 + 4 + 2 * kDeltaStages + 2 * kNumABuf + 2];
   __shared__ WinS s_win[kMaxWin];
@@ -275,9 +282,9 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int base_stage_bytes = kATile + p.xb_bytes;
   const uint32_t s_base_ring = sbase;
   const uint32_t s_delta_ring = s_base_ring + p.base_stages * base_stage_bytes;
-  const uint32_t s_abuf = s_delta_ring + kDeltaStages * kDeltaStageBytes;
+  const uint32_t s_abuf = s_delta_ring + p.delta_stages * kDeltaStageBytes;
   uint8_t* const g_delta_ring = sgen + p.base_stages * base_stage_bytes;
-  uint8_t* const g_abuf = g_delta_ring + kDeltaStages * kDeltaStageBytes;
+  uint8_t* const g_abuf = g_delta_ring + p.delta_stages * kDeltaStageBytes;
 
   uint64_t* bar_base_full = s_bars;
   uint64_t* bar_base_empty = s_bars + 4;
@@ -302,12 +309,14 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(smem_u32(&bar_a_free[i]), 1);
     }
     mbar_init(smem_u32(bar_acc_full), 1);
-    mbar_init(smem_u32(bar_acc_empty), 128);
+    mbar_init(smem_u32(bar_acc_empty), 128 * kNumWG);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x32) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xc) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -355,9 +364,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_expect_tx(full, kATile + p.xb_bytes);
             const uint32_t dstA = s_base_ring + sb * base_stage_bytes;
             tma_load_2d(dstA, &map_w, k0 + h * kBlockK, n0, full);
-            for (int rb = 0; rb < p.cols / 16; ++rb)
-              tma_load_2d(dstA + kATile + rb * 2048, &map_x, k0 + h * kBlockK, p.row0 + rb * 16,
-                          full);
+            tma_load_2d(dstA + kATile, &map_xc, k0 + h * kBlockK, p.row0, full);
             if (++sb == p.base_stages) { sb = 0; pb ^= 1; }
           }
           for (int w = 0; w < nwin; ++w) {
@@ -375,10 +382,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             bulk_load(dst + kRawBytes, p.meta + (size_t)ws.slot * p.mstride + blk * kMetaBlockBytes,
                       meta_bytes, full);
             for (int h = 0; h < nhalf; ++h)
-              for (int rb = 0; rb < ws.ncols / 16; ++rb)
-                tma_load_2d(dst + kRawBytes + kMetaBytes + h * ws.ncols * 128 + rb * 2048, &map_x,
-                            k0 + h * kBlockK, p.row0 + ws.col0 + rb * 16, full);
-            if (++sd == kDeltaStages) { sd = 0; pd ^= 1; }
+              tma_load_2d(dst + kRawBytes + kMetaBytes + h * ws.ncols * 128,
+                          ws.ncols == 16 ? &map_x : &map_x32, k0 + h * kBlockK,
+                          p.row0 + ws.col0, full);
+            if (++sd == p.delta_stages) { sd = 0; pd ^= 1; }
           }
         }
         u += ku1 - ku0;
@@ -433,7 +440,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             umma_commit(smem_u32(&bar_a_free[ab]));
             umma_commit(smem_u32(&bar_d_empty[sd]));
             if (++ab == kNumABuf) { ab = 0; pa ^= 1; }
-            if (++sd == kDeltaStages) { sd = 0; pdm ^= 1; }
+            if (++sd == p.delta_stages) { sd = 0; pdm ^= 1; }
           }
         }
         umma_commit(smem_u32(bar_acc_full));
@@ -441,12 +448,15 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   } else {
-    // ================= code expansion + epilogue (warps 2..5) =================
+    // ================= code expansion + epilogue (warps 2..) =================
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
     const int r = q * 32 + lane;         // tile row == TMEM lane
-    const int wg_tid = threadIdx.x - 64;
+    const int wg = (warp - 2) >> 2;      // warpgroup index
+    const int wg_tid = (threadIdx.x - 64) & 127;
+    const int ep_tid = threadIdx.x - 64;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    int sd = 0, pd = 0, ab = 0, pa = 1, pacc = 0;
+    const int ab = wg;                   // this warpgroup's expanded-A buffer
+    int sd = 0, pd = 0, pa = 1, pacc = 0, seq = 0;
     bool cta_first_fragment = true;
     const __half2 kBias = __half2half2(__ushort_as_half((unsigned short)(BITS == 4 ? 0x6408 : 0x6402)));
 
@@ -458,6 +468,14 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int k0 = ku * kUnitK;
         const int nhalf = min(2, (p.K - k0) / kBlockK);
         for (int w = 0; w < nwin; ++w) {
+          if ((seq++ % kNumWG) != wg) {  // another warpgroup's stage
+            // Still observe its "full" phase: a parity wait can only tell the
+            // current phase from the previous one, so every consumer has to see
+            // every phase of a ring slot in order.
+            mbar_wait(smem_u32(&bar_d_full[sd]), pd, abort_flag, p.status);
+            if (++sd == p.delta_stages) { sd = 0; pd ^= 1; }
+            continue;
+          }
           const WinS ws = s_win[w];
           const __half sc = *reinterpret_cast<const __half*>(p.scales + (size_t)ws.slot * p.sstride +
                                                              (size_t)(n0 + r) * 2);
@@ -467,7 +485,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint8_t* raw = g_delta_ring + sd * kDeltaStageBytes;
           uint8_t* arow = g_abuf + ab * kATile + r * 128;
           uint32_t mw[4] = {0, 0, 0, 0};
-          for (int h = 0; h < nhalf; ++h) {
+          for (int h = 0; h < ((p.debug & 1) ? 0 : nhalf); ++h) {
             if (BITS == 4) {
               const uint4 cw = *reinterpret_cast<const uint4*>(raw + h * 2048 + r * 16);
               const uint32_t wv[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -513,7 +531,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           {
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
             uint8_t* winb = const_cast<uint8_t*>(raw) + kRawBytes + kMetaBytes;
-            const int total = nhalf * ws.ncols * 8;
+            const int total = (p.debug & 2) ? 0 : nhalf * ws.ncols * 8;
             for (int idx = wg_tid; idx < total; idx += 128) {
               const int row = (idx >> 3) % ws.ncols;
               if (row < lo || row >= hi)
@@ -523,8 +541,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           fence_proxy_async();
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_a_ready[ab]));
-          if (++ab == kNumABuf) { ab = 0; pa ^= 1; }
-          if (++sd == kDeltaStages) { sd = 0; pd ^= 1; }
+          pa ^= 1;
+          if (++sd == p.delta_stages) { sd = 0; pd ^= 1; }
         }
       }
 
@@ -535,7 +553,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const bool full_tile = (ku0 == 0 && ku1 == KU);
       float* my_partial = p.partials +
                           ((size_t)cta * 2 + (cta_first_fragment ? 0 : 1)) * ((size_t)p.cols * 128);
-      for (int c = 0; c < p.cols / 16; ++c) {
+      for (int c = wg; c < p.cols / 16; c += kNumWG) {
         uint32_t v[16];
         tmem_ld16(lane_addr + c * 16, v);
         if (full_tile) {
@@ -562,30 +580,40 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int c_last = cta_of_unit((long long)(tile + 1) * KU - 1, p.grid, p.total_units);
         const int nfrag = c_last - c_first + 1;
         __threadfence();
-        named_bar_sync(1, 128);
-        if (wg_tid == 0) {
+        named_bar_sync(1, 128 * kNumWG);
+        if (ep_tid == 0) {
           const int old = atomicAdd(&p.counters[tile], 1);
           s_last = (old == nfrag - 1) ? 1 : 0;
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 128 * kNumWG);
         if (s_last) {
           __threadfence();
-          for (int col = 0; col < p.cols; ++col) {
-            const int prow = p.row0 + col;
-            if (prow >= p.M) break;
-            float sum = 0.f;
+          // 8 columns per pass so that eight independent L2 loads are in flight
+          // per fragment (a column-at-a-time loop is a chain of L2 latencies)
+          for (int cb = wg * 8; cb < p.cols; cb += kNumWG * 8) {
+            float sum[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[i] = 0.f;
             for (int f = 0; f < nfrag; ++f) {
               const int cc = c_first + f;
               const int cu0 = (int)((long long)cc * U / p.grid);
               const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
-              sum += __ldcg(p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)col * 128 + r);
+              const float* src = p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)cb * 128 + r;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + i * 128);
             }
-            const int tok = perm ? perm[prow] : prow;
-            p.y[(size_t)tok * p.N + n0 + r] = __float2half_rn(sum);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int prow = p.row0 + cb + i;
+              if (prow < p.M) {
+                const int tok = perm ? perm[prow] : prow;
+                p.y[(size_t)tok * p.N + n0 + r] = __float2half_rn(sum[i]);
+              }
+            }
           }
-          if (wg_tid == 0) p.counters[tile] = 0;
+          if (ep_tid == 0) p.counters[tile] = 0;
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 128 * kNumWG);
       }
       cta_first_fragment = false;
       u += ku1 - ku0;
@@ -646,7 +674,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // fp16 row-major [rows, K] matrix, box = 64 (k) x box_rows, 128-byte swizzle
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+int encode_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return DZ_ERR_CUDA;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -657,6 +685,34 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? DZ_OK : DZ_ERR_CUDA;
+}
+
+// Tensor maps depend only on (pointer, rows, K, box): a small per-thread cache
+// keeps the driver's encode call off the per-layer launch path.
+struct MapKey {
+  const void* ptr;
+  int rows, K, box;
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+};
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  constexpr int kEntries = 1024;
+  static thread_local MapEntry* cache = nullptr;
+  if (!cache) cache = new MapEntry[kEntries]();
+  const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
+  MapEntry& e = cache[(h >> 40) % kEntries ^ (box_rows & 7)];
+  if (e.key.ptr == ptr && e.key.rows == rows && e.key.K == K && e.key.box == box_rows) {
+    *map = e.map;
+    return DZ_OK;
+  }
+  int rc = encode_map(map, ptr, rows, K, box_rows);
+  if (rc == DZ_OK) {
+    e.key = MapKey{ptr, rows, K, box_rows};
+    e.map = *map;
+  }
+  return rc;
 }
 
 struct DeviceInfo {
@@ -705,10 +761,12 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     xsrc = xs;
   }
 
-  CUtensorMap map_w, map_x;
+  CUtensorMap map_w, map_x, map_x32, map_xc;
   int rc = make_map(&map_w, a.w_base, a.N, a.K, 128);
   if (rc) return rc;
   rc = make_map(&map_x, xsrc, a.M, a.K, 16);
+  if (rc) return rc;
+  rc = make_map(&map_x32, xsrc, a.M, a.K, 32);
   if (rc) return rc;
 
   Params p;
@@ -717,6 +775,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.num_kunits = (a.K + kUnitK - 1) / kUnitK;
   p.num_tiles = a.N / kTileN;
   p.base_only = base_only ? 1 : 0;
+  { const char* e = getenv("DZ_DEBUG"); p.debug = e ? atoi(e) : 0; }
   p.tokens_sorted = sorted ? 1 : 0;
   p.total_units = p.num_tiles * p.num_kunits;
   p.grid = min(min(di.sms, kMaxCtas), p.total_units);
@@ -737,15 +796,18 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     p.row0 = tb * kTokenBlock;
     p.cols = min(kTokenBlock, round_up(a.M - p.row0, 16));
     p.xb_bytes = p.cols * 128;
-    p.base_stages = max(1, min(4, kBaseRingBytes / (kATile + p.xb_bytes)));
+    p.base_stages = max(2, min(4, kBaseRingBytes / (kATile + p.xb_bytes)));
+    p.delta_stages = p.cols <= 64 ? 5 : (p.cols <= 128 ? 4 : 3);
+    rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols);
+    if (rc) return rc;
     const size_t smem = (size_t)p.base_stages * (kATile + p.xb_bytes) +
-                        (size_t)kDeltaStages * kDeltaStageBytes + (size_t)kNumABuf * kATile + 1024;
+                        (size_t)p.delta_stages * kDeltaStageBytes + (size_t)kNumABuf * kATile + 1024;
     auto kern = (a.bits == 2) ? sbmm_tc_kernel<2> : sbmm_tc_kernel<4>;
     if (!di.attr_set[bits_idx]) {
-      DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+      DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024));
       di.attr_set[bits_idx] = true;
     }
-    kern<<<p.grid, kThreads, smem, st>>>(map_w, map_x, p);
+    kern<<<p.grid, kThreads, smem, st>>>(map_w, map_x, map_x32, map_xc, p);
     DZ_CUDA_OK(cudaGetLastError());
   }
   return DZ_OK;

@@ -72,3 +72,19 @@ def test_converter_flags_asymmetric_zero_point():
     with pytest.raises(DeltaZipError) as e:
         ops.convert_from_gptq(_to_dev(qw), _to_dev(qz), _to_dev(sc), 4)
     assert e.value.status == _lib.DZ_ERR_NOT_SYMMETRIC
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_gpu_compressor_matches_oracle(bits):
+    """The torch-op compressor used to build benchmark-size inputs produces the
+    same GPTQ tensors as the oracle's restatement of the reference pipeline."""
+    from deltazip_b200 import synth
+    rng = np.random.default_rng(5)
+    d = rng.standard_normal((256, 512), dtype=np.float32) * np.float32(1e-3)
+    d[3] = 0
+    wq, scale, zero = O.compress_delta(d, bits)
+    qw, qz, sc = O.pack(wq, scale, zero, bits)
+    gqw, gqz, gsc = synth.compress_delta_gptq(_to_dev(d), bits)
+    np.testing.assert_array_equal(gqw.cpu().numpy(), qw)
+    np.testing.assert_array_equal(gqz.cpu().numpy(), qz)
+    np.testing.assert_array_equal(gsc.cpu().numpy().view(np.uint16), sc.view(np.uint16))

@@ -80,3 +80,24 @@ def test_apply_delta_semantics():
         if idx[i] >= 0:
             yi = (yi + O.delta_forward(x[i:i + 1], *deltas[idx[i]])).astype(np.float16)
         np.testing.assert_array_equal(y[i:i + 1].view(np.uint16), yi.view(np.uint16))
+
+
+def test_torch_port_matches_golden(case):
+    """The torch-CPU port (the timed CPU baseline) reproduces the reference's
+    unpacked delta bit for bit and its layer output within accumulation noise."""
+    import torch
+    from oracle import torch_port as T
+    bits = int(case["bits"])
+    dt = T.dequantize(torch.from_numpy(case["qweight"]), torch.from_numpy(case["qzeros"]),
+                      torch.from_numpy(case["scales"]), bits)
+    np.testing.assert_array_equal(dt.t().contiguous().numpy().view(np.uint16),
+                                  case["dense"].view(np.uint16))
+    x = torch.from_numpy(case["x"])
+    idx = torch.zeros(x.shape[0], dtype=torch.int64)
+    idx[0] = -1
+    y = T.apply_delta(x, torch.from_numpy(case["w_base"]),
+                      [(torch.from_numpy(case["qweight"]), torch.from_numpy(case["qzeros"]),
+                        torch.from_numpy(case["scales"]), bits)], idx).numpy()
+    ref = (case["y_base"].astype(np.float32) + case["y_delta"].astype(np.float32))
+    ref[0] = case["y_base"][0]
+    assert O.rel_l2(y, ref) <= 3e-3
