@@ -5,15 +5,22 @@
 // (TMEM lanes), the tokens of a token block (<= 256, sorted by slot) are its N
 // dimension (TMEM columns), so a decode batch never pads M up to 128 and every
 // weight byte is streamed from HBM exactly once.
-//   base  : A = W tile [128 x 64] fp16 (TMA, 128B swizzle), B = x tile
-//           [cols x 64] (TMA), dense tcgen05.mma, N = cols.
+//   base  : A = W tile [128 x 64] fp16 (TMA, 128B swizzle), B = x half-tile
+//           [cols x 64] (TMA), dense tcgen05.mma (SS), N = cols.
 //   delta : the packed codes and 2:4 metadata of (slot, tile, k-unit) arrive by
-//           bulk copy; four warps expand the codes to the *compressed* fp16 A
-//           operand in swizzled shared memory (one row per thread, one logic op
-//           + one subtract + one multiply per fp16 pair), copy the metadata
-//           into tensor memory, and zero the rows of the slot's token window
-//           that belong to other slots; tcgen05.mma.sp then accumulates into
-//           the window's columns of the SAME accumulator the base product used.
+//           bulk copy; a warpgroup expands the codes to the *compressed* fp16 A
+//           operand directly into tensor memory (one row per thread, one logic
+//           op + one subtract + one multiply per fp16 pair, tcgen05.st), stores
+//           the metadata next to it, and copies the slot's token window out of
+//           the resident x tile with the rows of other slots zeroed;
+//           tcgen05.mma.sp (A and metadata in TMEM, B in shared memory) then
+//           accumulates into the window's columns of the SAME accumulator the
+//           base product used.
+//
+// Shared memory holds four rings sized for what feeds them: W tiles and packed
+// delta stages come from HBM and are kept deep, x half-tiles come from L2 and
+// stay resident for the whole k-unit so that every window is cut from them
+// without another load.
 //
 // Work split.  (tile, k-unit of 128) pairs are divided evenly over one CTA per
 // SM ("stream-K"): a CTA walks a contiguous unit range, which may cover the
@@ -22,19 +29,17 @@
 // fragment of a tile to finish (a per-tile counter) adds the partials in fixed
 // order, so results do not depend on timing.
 //
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, then four
-// warpgroups of 128 threads that expand codes (delta stage s goes to warpgroup
-// s mod 4, so several stages are expanded at once and each scheduler has four
-// warps to hide latency with) and share the epilogue by column chunks.
+// Warp roles: warp 0 = TMA producer for W and x, warp 1 = MMA issuer and TMEM
+// owner, warp 2 = bulk-copy producer for packed delta stages, warp 3 idle, then
+// four warpgroups of 128 threads that expand codes (delta stage s goes to
+// warpgroup s mod 4) and share the epilogue by column chunks.
 // Every mbarrier wait is bounded: on a timeout the CTA records DZ_ERR_TIMEOUT,
 // raises an abort flag that turns every later wait into a no-op, runs its
 // (bounded) loops to the end and frees its tensor memory.
 #include <cuda.h>
-
 #include <stdlib.h>
 
 #include <mutex>
-#include <unordered_map>
 
 #include "dz_common.cuh"
 
@@ -43,32 +48,33 @@ namespace dz {
 namespace {
 
 constexpr int kNumWG = 4;                      // code-expansion warpgroups (128 threads each)
-constexpr int kThreads = 64 + 128 * kNumWG;
+constexpr int kFirstWGWarp = 4;
+constexpr int kThreads = 32 * kFirstWGWarp + 128 * kNumWG;
 constexpr int kUnitK = 128;                    // dense k per work unit
-constexpr int kATile = 128 * 128;              // bytes: 128 rows x 128 B
-constexpr int kNumABuf = kNumWG;               // expanded-A buffers, one per warpgroup
-constexpr int kDeltaStages = 6;                // upper bound; Params::delta_stages are used
+constexpr int kWTile = 128 * 128;              // bytes: 128 rows x 128 B
 constexpr int kRawBytes = 4096;                // codes of one unit (4-bit)
 constexpr int kMetaBytes = 2048;               // metadata of one unit
-constexpr int kWinBytes = 2 * kMaxWindowCols * 128;
-constexpr int kDeltaStageBytes = kRawBytes + kMetaBytes + kWinBytes;
-constexpr int kBaseRingBytes = 72 * 1024;
+constexpr int kRStage = kRawBytes + kMetaBytes;
+constexpr int kWinBytes = 2 * kMaxWindowCols * 128;   // per-warpgroup window buffer
+constexpr int kMaxW = 4, kMaxX = 8, kMaxR = 16;
 constexpr int kMaxWin = 256;                   // windows of one token block
 constexpr int kTmemCols = 512;
-constexpr int kMetaCol = 256;                  // first TMEM column of the metadata buffers
+constexpr int kMaxBuf = 8;                     // expanded-A / metadata / window buffers in flight
+// TMEM columns: accumulator [0, dcols), then 32 columns of expanded A per buffer,
+// then 4 columns of metadata per buffer (dcols = 128 -> 8 buffers, 256 -> 4).
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
 constexpr int kMaxCtas = 160;
-
-static_assert(kDeltaStageBytes % 1024 == 0, "stage regions stay 1024-byte aligned");
+constexpr int kSmemBudget = 216 * 1024;
 
 struct Params {
   int M, N, K, bits;
   int num_kunits, num_tiles, num_kblocks;
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
   int base_only, tokens_sorted;
-  int debug;   // experiment switches (bit 0: skip code expansion, bit 1: skip window zeroing)
+  int debug;
   int grid, total_units;
-  int base_stages, delta_stages, xb_bytes;
+  int w_stages, x_stages, r_stages, xb_bytes;
+  int nbuf, dcols;
   const uint8_t* qweight;
   const uint8_t* meta;
   const uint8_t* scales;
@@ -132,6 +138,20 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+// Wait with an inlined first probe; with INSTR the cycles spent are accounted
+// (experiments only).
+template <bool INSTR>
+__device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int* status, long long& acc) {
+  if (INSTR) {
+    const long long t0 = clock64();
+    mbar_wait(bar, parity, abort_flag, status);
+    acc += clock64() - t0;
+  } else {
+    if (mbar_try_wait(bar, parity)) return;
+    mbar_wait(bar, parity, abort_flag, status);
+  }
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
                                             uint32_t bar) {
   asm volatile(
@@ -180,12 +200,74 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void umma_ss_sp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+// 2:4-sparse MMA, compressed A and its metadata both in tensor memory
+__device__ __forceinline__ void umma_ts_sp(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
                                            uint32_t e_tmem, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], [%1], %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Descriptors are handled as (lo, hi) 32-bit halves: hi is the same for every
+// K-major 128B-swizzled tile, lo carries the start address.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) {
+  return ((saddr >> 4) & 0x3FFFu) | (1u << 16);
+}
+// four dense MMAs over one 64-wide k half-tile (k advances 32 B = 2 descriptor units)
+__device__ __forceinline__ void umma_ss_x4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .b64 da, db;\n\t"
+      ".reg .b32 al, bl;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 q, %5, %5;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "add.u32 al, %1, 2;\n\t"
+      "add.u32 bl, %2, 2;\n\t"
+      "mov.b64 da, {al, %3};\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+      "add.u32 al, %1, 4;\n\t"
+      "add.u32 bl, %2, 4;\n\t"
+      "mov.b64 da, {al, %3};\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+      "add.u32 al, %1, 6;\n\t"
+      "add.u32 bl, %2, 6;\n\t"
+      "mov.b64 da, {al, %3};\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// two 2:4-sparse MMAs over one 64-wide k half of a window: compressed A
+// (8 TMEM columns each) and metadata (one column each, addressed as the even
+// column of the pair + sparsity selector) in tensor memory, B in shared memory
+// (k advances 64 B = 4 descriptor units)
+__device__ __forceinline__ void umma_ts_sp_x2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                              uint32_t e_tmem, uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      ".reg .b64 db;\n\t"
+      ".reg .b32 bl, a1, i1;\n\t"
+      "setp.eq.b32 q, %1, %1;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], [%1], db, [%3], %4, q;\n\t"
+      "add.u32 bl, %2, 4;\n\t"
+      "add.u32 a1, %1, 8;\n\t"
+      "or.b32 i1, %4, 1;\n\t"
+      "mov.b64 db, {bl, %5};\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], [a1], db, [%3], i1, q;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(e_tmem), "r"(idesc), "r"(kDescHi)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -204,11 +286,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c,
                                          uint32_t d) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr),
                "r"(a), "r"(b), "r"(c), "r"(d)
                : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
@@ -224,10 +316,6 @@ __device__ __forceinline__ uint32_t extract_pair(uint32_t w, int shift) {
   return r;
 }
 
-struct Fragment {
-  int tile, ku0, ku1;
-};
-
 // CTA that owns unit u when `total` units are split evenly over `grid` CTAs
 // (CTA c owns [c*total/grid, (c+1)*total/grid)).
 __device__ __forceinline__ int cta_of_unit(long long u, int grid, int total) {
@@ -238,22 +326,29 @@ struct WinS {
   int slot, col0, ncols, lohi;  // col0 relative to the token block; lohi = lo | hi << 16 (relative)
 };
 
+struct Ring {
+  int idx, par, size;
+  __device__ __forceinline__ Ring(int size_, int par0) : idx(0), par(par0), size(size_) {}
+  __device__ __forceinline__ void advance() {
+    if (++idx == size) { idx = 0; par ^= 1; }
+  }
+};
+
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int BITS>
+template <int BITS, bool INSTR>
 __global__ void __launch_bounds__(kThreads, 1)
-sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               const __grid_constant__ CUtensorMap map_x32,
-               const __grid_constant__ CUtensorMap map_xc, const Params p) {
+sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xc,
+               const Params p) {
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t s_bars[4 + 4 + 2 * kDeltaStages + 2 * kNumABuf + 2];
+  __shared__ __align__(8) uint64_t s_bars[2 * kMaxW + 2 * kMaxX + 2 * kMaxR + 2 * kMaxBuf + 2];
   __shared__ WinS s_win[kMaxWin];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_last;
 
   // ---- early uniform exits (before any barrier or TMEM state exists) ----
-  int nwin = 0, win_begin = 0;
+  int nwin = 0;
   const int* perm = nullptr;
   const Window* gwin = nullptr;
   if (p.seg) {
@@ -266,7 +361,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     perm = reinterpret_cast<const int*>(p.seg + lay.perm);
     if (!p.base_only) {
       const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
-      win_begin = bb[p.token_block];
+      const int win_begin = bb[p.token_block];
       nwin = min(bb[p.token_block + 1] - win_begin, kMaxWin);
       gwin = reinterpret_cast<const Window*>(p.seg + lay.windows) + win_begin;
     }
@@ -279,32 +374,42 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t dyn0 = smem_u32(smem_dyn);
   const uint32_t sbase = (dyn0 + 1023u) & ~1023u;
   uint8_t* const sgen = smem_dyn + (sbase - dyn0);
-  const int base_stage_bytes = kATile + p.xb_bytes;
-  const uint32_t s_base_ring = sbase;
-  const uint32_t s_delta_ring = s_base_ring + p.base_stages * base_stage_bytes;
-  const uint32_t s_abuf = s_delta_ring + p.delta_stages * kDeltaStageBytes;
-  uint8_t* const g_delta_ring = sgen + p.base_stages * base_stage_bytes;
-  uint8_t* const g_abuf = g_delta_ring + p.delta_stages * kDeltaStageBytes;
+  const uint32_t s_wring = sbase;
+  const uint32_t off_x = p.w_stages * kWTile;
+  const uint32_t off_win = off_x + p.x_stages * p.xb_bytes;
+  const uint32_t off_r = off_win + p.nbuf * kWinBytes;
+  const uint32_t s_xring = sbase + off_x;
+  const uint32_t s_winbuf = sbase + off_win;
+  const uint32_t s_rring = sbase + off_r;
+  uint8_t* const g_xring = sgen + off_x;
+  uint8_t* const g_winbuf = sgen + off_win;
+  uint8_t* const g_rring = sgen + off_r;
 
-  uint64_t* bar_base_full = s_bars;
-  uint64_t* bar_base_empty = s_bars + 4;
-  uint64_t* bar_d_full = s_bars + 8;
-  uint64_t* bar_d_empty = bar_d_full + kDeltaStages;
-  uint64_t* bar_a_ready = bar_d_empty + kDeltaStages;
-  uint64_t* bar_a_free = bar_a_ready + kNumABuf;
-  uint64_t* bar_acc_full = bar_a_free + kNumABuf;
+  uint64_t* bar_w_full = s_bars;
+  uint64_t* bar_w_empty = bar_w_full + kMaxW;
+  uint64_t* bar_x_full = bar_w_empty + kMaxW;
+  uint64_t* bar_x_empty = bar_x_full + kMaxX;
+  uint64_t* bar_r_full = bar_x_empty + kMaxX;
+  uint64_t* bar_r_empty = bar_r_full + kMaxR;
+  uint64_t* bar_a_ready = bar_r_empty + kMaxR;
+  uint64_t* bar_a_free = bar_a_ready + kMaxBuf;
+  uint64_t* bar_acc_full = bar_a_free + kMaxBuf;
   uint64_t* bar_acc_empty = bar_acc_full + 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(smem_u32(&bar_base_full[i]), 1);
-      mbar_init(smem_u32(&bar_base_empty[i]), 1);
+    for (int i = 0; i < kMaxW; ++i) {
+      mbar_init(smem_u32(&bar_w_full[i]), 1);
+      mbar_init(smem_u32(&bar_w_empty[i]), 1);
     }
-    for (int i = 0; i < kDeltaStages; ++i) {
-      mbar_init(smem_u32(&bar_d_full[i]), 1);
-      mbar_init(smem_u32(&bar_d_empty[i]), 1);
+    for (int i = 0; i < kMaxX; ++i) {
+      mbar_init(smem_u32(&bar_x_full[i]), 1);
+      mbar_init(smem_u32(&bar_x_empty[i]), 1);
     }
-    for (int i = 0; i < kNumABuf; ++i) {
+    for (int i = 0; i < kMaxR; ++i) {
+      mbar_init(smem_u32(&bar_r_full[i]), 1);
+      mbar_init(smem_u32(&bar_r_empty[i]), 128);
+    }
+    for (int i = 0; i < kMaxBuf; ++i) {
       mbar_init(smem_u32(&bar_a_ready[i]), 128);
       mbar_init(smem_u32(&bar_a_free[i]), 1);
     }
@@ -314,8 +419,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x32) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xc) : "memory");
   }
   if (warp == 1) {
@@ -348,9 +451,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int KU = p.num_kunits;
 
   if (warp == 0) {
-    // =========================== TMA producer ===========================
+    // ====================== TMA producer: W tiles and x half-tiles ======================
     if (lane == 0) {
-      int sb = 0, pb = 1, sd = 0, pd = 1;
+      Ring rw(p.w_stages, 1), rx(p.x_stages, 1);
+      long long t_w = 0;
+      const long long t_start = clock64();
       for (int u = u_begin; u < u_end;) {
         const int tile = u / KU, ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
@@ -359,195 +464,245 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const int k0 = ku * kUnitK;
           const int nhalf = min(2, (p.K - k0) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
-            mbar_wait(smem_u32(&bar_base_empty[sb]), pb, abort_flag, p.status);
-            const uint32_t full = smem_u32(&bar_base_full[sb]);
-            mbar_expect_tx(full, kATile + p.xb_bytes);
-            const uint32_t dstA = s_base_ring + sb * base_stage_bytes;
-            tma_load_2d(dstA, &map_w, k0 + h * kBlockK, n0, full);
-            tma_load_2d(dstA + kATile, &map_xc, k0 + h * kBlockK, p.row0, full);
-            if (++sb == p.base_stages) { sb = 0; pb ^= 1; }
-          }
-          for (int w = 0; w < nwin; ++w) {
-            const WinS ws = s_win[w];
-            mbar_wait(smem_u32(&bar_d_empty[sd]), pd, abort_flag, p.status);
-            const uint32_t full = smem_u32(&bar_d_full[sd]);
-            const uint32_t code_bytes = nhalf * codes_block_bytes(BITS);
-            const uint32_t meta_bytes = nhalf * kMetaBlockBytes;
-            const uint32_t win_bytes = nhalf * ws.ncols * 128;
-            mbar_expect_tx(full, code_bytes + meta_bytes + win_bytes);
-            const size_t blk = (size_t)tile * p.num_kblocks + (size_t)ku * 2;
-            const uint32_t dst = s_delta_ring + sd * kDeltaStageBytes;
-            bulk_load(dst, p.qweight + (size_t)ws.slot * p.qstride + blk * codes_block_bytes(BITS),
-                      code_bytes, full);
-            bulk_load(dst + kRawBytes, p.meta + (size_t)ws.slot * p.mstride + blk * kMetaBlockBytes,
-                      meta_bytes, full);
-            for (int h = 0; h < nhalf; ++h)
-              tma_load_2d(dst + kRawBytes + kMetaBytes + h * ws.ncols * 128,
-                          ws.ncols == 16 ? &map_x : &map_x32, k0 + h * kBlockK,
-                          p.row0 + ws.col0, full);
-            if (++sd == p.delta_stages) { sd = 0; pd ^= 1; }
+            mbar_wait_t<INSTR>(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status, t_w);
+            const uint32_t xfull = smem_u32(&bar_x_full[rx.idx]);
+            mbar_expect_tx(xfull, p.xb_bytes);
+            tma_load_2d(s_xring + rx.idx * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
+            rx.advance();
+            mbar_wait_t<INSTR>(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status, t_w);
+            const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
+            mbar_expect_tx(wfull, kWTile);
+            tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+            rw.advance();
           }
         }
         u += ku1 - ku0;
+      }
+      if (p.debug & 16) {
+        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
+        atomicAdd(st + 11, (unsigned long long)(clock64() - t_start));
+        atomicAdd(st + 12, (unsigned long long)t_w);
+      }
+    }
+  } else if (warp == 2) {
+    // ====================== bulk-copy producer: packed delta stages ======================
+    if (lane == 0 && nwin > 0) {
+      Ring rr(p.r_stages, 1);
+      long long t_w = 0;
+      const long long t_start = clock64();
+      for (int u = u_begin; u < u_end;) {
+        const int tile = u / KU, ku0 = u % KU;
+        const int ku1 = min(KU, ku0 + (u_end - u));
+        for (int ku = ku0; ku < ku1; ++ku) {
+          const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
+          const uint32_t code_bytes = nhalf * codes_block_bytes(BITS);
+          const uint32_t meta_bytes = nhalf * kMetaBlockBytes;
+          const size_t blk = (size_t)tile * p.num_kblocks + (size_t)ku * 2;
+          for (int w = 0; w < nwin; ++w) {
+            const int slot = s_win[w].slot;
+            mbar_wait_t<INSTR>(smem_u32(&bar_r_empty[rr.idx]), rr.par, abort_flag, p.status, t_w);
+            const uint32_t full = smem_u32(&bar_r_full[rr.idx]);
+            mbar_expect_tx(full, code_bytes + meta_bytes);
+            const uint32_t dst = s_rring + rr.idx * kRStage;
+            bulk_load(dst, p.qweight + (size_t)slot * p.qstride + blk * codes_block_bytes(BITS),
+                      code_bytes, full);
+            bulk_load(dst + kRawBytes, p.meta + (size_t)slot * p.mstride + blk * kMetaBlockBytes,
+                      meta_bytes, full);
+            rr.advance();
+          }
+        }
+        u += ku1 - ku0;
+      }
+      if (p.debug & 16) {
+        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
+        atomicAdd(st + 9, (unsigned long long)(clock64() - t_start));
+        atomicAdd(st + 10, (unsigned long long)t_w);
       }
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
-      int sb = 0, pb = 0, sd = 0, pdm = 0, ab = 0, pa = 0, pacc = 1;
+      Ring rw(p.w_stages, 0), rx(p.x_stages, 0);
+      uint32_t pa_bits = 0;   // bit b: parity of buffer b's "ready" barrier
+      const uint32_t a_col0 = tmem_base + p.dcols;
+      const uint32_t e_col0 = a_col0 + p.nbuf * 32;
+      int pacc = 1, seq = 0;
+      long long t_acc = 0, t_base = 0, t_ready = 0;
+      const long long t_start = clock64();
       const uint32_t idesc_base = make_idesc(p.cols, false);
       for (int u = u_begin; u < u_end;) {
         const int ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
-        mbar_wait(smem_u32(bar_acc_empty), pacc, abort_flag, p.status);
+        mbar_wait_t<INSTR>(smem_u32(bar_acc_empty), pacc, abort_flag, p.status, t_acc);
         pacc ^= 1;
         tc_fence_after();
         uint32_t acc = 0;
         for (int ku = ku0; ku < ku1; ++ku) {
           const int k0 = ku * kUnitK;
           const int nhalf = min(2, (p.K - k0) / kBlockK);
+          int xslot0 = 0, xslot1 = 0;
           for (int h = 0; h < nhalf; ++h) {
-            mbar_wait(smem_u32(&bar_base_full[sb]), pb, abort_flag, p.status);
+            mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_base);
+            mbar_wait_t<INSTR>(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status, t_base);
             tc_fence_after();
-            const uint32_t a0 = s_base_ring + sb * base_stage_bytes;
-            const uint64_t adesc = make_desc(a0);
-            const uint64_t bdesc = make_desc(a0 + kATile);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              umma_ss(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc_base, acc);
-              acc = 1;
-            }
-            umma_commit(smem_u32(&bar_base_empty[sb]));
-            if (++sb == p.base_stages) { sb = 0; pb ^= 1; }
+            if (h == 0) xslot0 = rx.idx; else xslot1 = rx.idx;
+            umma_ss_x4(tmem_base, desc_lo(s_wring + rw.idx * kWTile),
+                       desc_lo(s_xring + rx.idx * p.xb_bytes), idesc_base, acc);
+            acc = 1;
+            umma_commit(smem_u32(&bar_w_empty[rw.idx]));
+            rw.advance();
+            rx.advance();
           }
           for (int w = 0; w < nwin; ++w) {
             const WinS ws = s_win[w];
-            mbar_wait(smem_u32(&bar_d_full[sd]), pdm, abort_flag, p.status);
-            mbar_wait(smem_u32(&bar_a_ready[ab]), pa, abort_flag, p.status);
+            const int g = seq % p.nbuf;
+            ++seq;
+            mbar_wait_t<INSTR>(smem_u32(&bar_a_ready[g]), (pa_bits >> g) & 1u, abort_flag, p.status, t_ready);
+            pa_bits ^= 1u << g;
             tc_fence_after();
-            const uint64_t adesc = make_desc(s_abuf + ab * kATile);
-            const uint32_t winb = s_delta_ring + sd * kDeltaStageBytes + kRawBytes + kMetaBytes;
+            const uint32_t win_lo = desc_lo(s_winbuf + g * kWinBytes);
             const uint32_t idesc = make_idesc(ws.ncols, true);
             const uint32_t dcol = tmem_base + ws.col0;
-            const uint32_t ecol = tmem_base + kMetaCol + ab * 4;
-            for (int j = 0; j < nhalf * 2; ++j) {
-              const uint64_t bdesc = make_desc(winb + (j >> 1) * ws.ncols * 128) + 4 * (j & 1);
-              // metadata of MMA j sits in column j of the buffer; the instruction
-              // takes the even column of the pair and selects inside it with the
-              // descriptor's sparsity-selector bits
-              umma_ss_sp(dcol, adesc + 2 * j, bdesc, ecol + (j & ~1), idesc | (uint32_t)(j & 1), 1u);
+            const uint32_t acol = a_col0 + g * 32;
+            const uint32_t ecol = e_col0 + g * 4;
+            if (!(p.debug & 4)) {
+              umma_ts_sp_x2(dcol, acol, win_lo, ecol, idesc);
+              if (nhalf == 2) umma_ts_sp_x2(dcol, acol + 16, win_lo + ws.ncols * 8, ecol + 2, idesc);
             }
-            umma_commit(smem_u32(&bar_a_free[ab]));
-            umma_commit(smem_u32(&bar_d_empty[sd]));
-            if (++ab == kNumABuf) { ab = 0; pa ^= 1; }
-            if (++sd == p.delta_stages) { sd = 0; pdm ^= 1; }
+            umma_commit(smem_u32(&bar_a_free[g]));
           }
+          // the unit's x half-tiles are free once every MMA above has read them
+          umma_commit(smem_u32(&bar_x_empty[xslot0]));
+          if (nhalf == 2) umma_commit(smem_u32(&bar_x_empty[xslot1]));
         }
         umma_commit(smem_u32(bar_acc_full));
         u += ku1 - ku0;
       }
+      if (p.debug & 16) {
+        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
+        atomicAdd(st + 0, (unsigned long long)(clock64() - t_start));
+        atomicAdd(st + 1, (unsigned long long)t_acc);
+        atomicAdd(st + 2, (unsigned long long)t_base);
+        atomicAdd(st + 3, (unsigned long long)t_ready);
+      }
     }
-  } else {
-    // ================= code expansion + epilogue (warps 2..) =================
+  } else if (warp >= kFirstWGWarp) {
+    // ================= code expansion + epilogue =================
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
     const int r = q * 32 + lane;         // tile row == TMEM lane
-    const int wg = (warp - 2) >> 2;      // warpgroup index
-    const int wg_tid = (threadIdx.x - 64) & 127;
-    const int ep_tid = threadIdx.x - 64;
+    const int wg = (warp - kFirstWGWarp) >> 2;
+    const int wg_tid = (threadIdx.x - 32 * kFirstWGWarp) & 127;
+    const int ep_tid = threadIdx.x - 32 * kFirstWGWarp;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int ab = wg;                   // this warpgroup's expanded-A buffer
-    int sd = 0, pd = 0, pa = 1, pacc = 0, seq = 0;
+    Ring rr(p.r_stages, 0), rx(p.x_stages, 0);
+    uint32_t pa_bits = 0xFFu;   // bit b: parity of buffer b's "free" barrier
+    int pacc = 0, seq = 0;
+    const uint32_t a_col0 = lane_addr + p.dcols;
+    const uint32_t e_col0 = a_col0 + p.nbuf * 32;
     bool cta_first_fragment = true;
+    long long t_rfull = 0, t_afree = 0, t_xfull = 0, t_accf = 0;
+    const long long t_start = clock64();
     const __half2 kBias = __half2half2(__ushort_as_half((unsigned short)(BITS == 4 ? 0x6408 : 0x6402)));
 
     for (int u = u_begin; u < u_end;) {
       const int tile = u / KU, ku0 = u % KU;
       const int ku1 = min(KU, ku0 + (u_end - u));
       const int n0 = tile * kTileN;
-      for (int ku = ku0; ku < ku1; ++ku) {
+      for (int ku = ku0; ku < ku1 && nwin > 0; ++ku) {
         const int k0 = ku * kUnitK;
         const int nhalf = min(2, (p.K - k0) / kBlockK);
+        // the unit's x half-tiles (every warpgroup observes every phase in order)
+        const uint8_t* xsrc0 = nullptr;
+        const uint8_t* xsrc1 = nullptr;
+        for (int h = 0; h < nhalf; ++h) {
+          mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_xfull);
+          if (h == 0) xsrc0 = g_xring + rx.idx * p.xb_bytes; else xsrc1 = g_xring + rx.idx * p.xb_bytes;
+          rx.advance();
+        }
         for (int w = 0; w < nwin; ++w) {
+          const int buf = seq % p.nbuf;
           if ((seq++ % kNumWG) != wg) {  // another warpgroup's stage
-            // Still observe its "full" phase: a parity wait can only tell the
-            // current phase from the previous one, so every consumer has to see
-            // every phase of a ring slot in order.
-            mbar_wait(smem_u32(&bar_d_full[sd]), pd, abort_flag, p.status);
-            if (++sd == p.delta_stages) { sd = 0; pd ^= 1; }
+            // The ring sizes are multiples of the warpgroup count, so a ring slot
+            // (and an expanded-A buffer) is only ever used by one warpgroup, which
+            // therefore sees each of its phases in order -- a parity wait cannot
+            // tell phase n from phase n + 2.
+            rr.advance();
             continue;
           }
           const WinS ws = s_win[w];
           const __half sc = *reinterpret_cast<const __half*>(p.scales + (size_t)ws.slot * p.sstride +
                                                              (size_t)(n0 + r) * 2);
           const __half2 sc2 = __half2half2(sc);
-          mbar_wait(smem_u32(&bar_d_full[sd]), pd, abort_flag, p.status);
-          mbar_wait(smem_u32(&bar_a_free[ab]), pa, abort_flag, p.status);
-          const uint8_t* raw = g_delta_ring + sd * kDeltaStageBytes;
-          uint8_t* arow = g_abuf + ab * kATile + r * 128;
+          mbar_wait_t<INSTR>(smem_u32(&bar_r_full[rr.idx]), rr.par, abort_flag, p.status, t_rfull);
+          mbar_wait_t<INSTR>(smem_u32(&bar_a_free[buf]), (pa_bits >> buf) & 1u, abort_flag, p.status, t_afree);
+          pa_bits ^= 1u << buf;
+          uint8_t* const my_win = g_winbuf + buf * kWinBytes;
+          tc_fence_after();
+          const uint8_t* raw = g_rring + rr.idx * kRStage;
           uint32_t mw[4] = {0, 0, 0, 0};
-          for (int h = 0; h < ((p.debug & 1) ? 0 : nhalf); ++h) {
-            if (BITS == 4) {
+          for (int h = 0; h < nhalf; ++h) {
+            uint32_t o[16];
+            if (p.debug & 1) {  // experiment: no code expansion, A := 0 (metadata stays valid)
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = 0;
+            } else if (BITS == 4) {
               const uint4 cw = *reinterpret_cast<const uint4*>(raw + h * 2048 + r * 16);
               const uint32_t wv[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
-              for (int wi = 0; wi < 4; ++wi) {
-                uint32_t o[4];
+              for (int wi = 0; wi < 4; ++wi)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   uint32_t t = extract_pair<0x000f000fu>(wv[wi], 4 * j);
                   __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), kBias), sc2);
-                  o[j] = *reinterpret_cast<uint32_t*>(&hv);
+                  o[wi * 4 + j] = *reinterpret_cast<uint32_t*>(&hv);
                 }
-                const int c = h * 4 + wi;
-                *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(o[0], o[1], o[2], o[3]);
-              }
             } else {
               const uint2 cw = *reinterpret_cast<const uint2*>(raw + h * 1024 + r * 8);
               const uint32_t wv[2] = {cw.x, cw.y};
 #pragma unroll
-              for (int wi = 0; wi < 2; ++wi) {
+              for (int wi = 0; wi < 2; ++wi)
 #pragma unroll
-                for (int half8 = 0; half8 < 2; ++half8) {
-                  uint32_t o[4];
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    uint32_t t = extract_pair<0x00030003u>(wv[wi], 2 * (half8 * 4 + j));
-                    __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), kBias), sc2);
-                    o[j] = *reinterpret_cast<uint32_t*>(&hv);
-                  }
-                  const int c = h * 4 + wi * 2 + half8;
-                  *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) =
-                      make_uint4(o[0], o[1], o[2], o[3]);
+                for (int j = 0; j < 8; ++j) {
+                  uint32_t t = extract_pair<0x00030003u>(wv[wi], 2 * j);
+                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), kBias), sc2);
+                  o[wi * 8 + j] = *reinterpret_cast<uint32_t*>(&hv);
                 }
-              }
             }
+            // compressed A of this half: 32 fp16 = 16 columns of the row's lane
+            tmem_st16(a_col0 + buf * 32 + h * 16, o);
             const uint2 m2 = *reinterpret_cast<const uint2*>(raw + kRawBytes + h * 1024 + r * 8);
             mw[h * 2] = m2.x;
             mw[h * 2 + 1] = m2.y;
           }
-          tmem_st4(lane_addr + kMetaCol + ab * 4, mw[0], mw[1], mw[2], mw[3]);
-          // zero the window rows that belong to other slots
+          tmem_st4(e_col0 + buf * 4, mw[0], mw[1], mw[2], mw[3]);
+          // the packed stage has been consumed
+          mbar_arrive(smem_u32(&bar_r_empty[rr.idx]));
+          rr.advance();
+          // the slot's token window: rows of the resident x half-tiles, other slots' rows zeroed
           {
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
-            uint8_t* winb = const_cast<uint8_t*>(raw) + kRawBytes + kMetaBytes;
-            const int total = (p.debug & 2) ? 0 : nhalf * ws.ncols * 8;
+            const int per_half = ws.ncols * 8;           // 16-byte chunks
+            const int total = (p.debug & 2) ? 0 : nhalf * per_half;
             for (int idx = wg_tid; idx < total; idx += 128) {
-              const int row = (idx >> 3) % ws.ncols;
-              if (row < lo || row >= hi)
-                *reinterpret_cast<uint4*>(winb + (size_t)idx * 16) = make_uint4(0, 0, 0, 0);
+              const int h = idx >= per_half ? 1 : 0;
+              const int rem = idx - h * per_half;
+              const int row = rem >> 3;
+              uint4 v = make_uint4(0, 0, 0, 0);
+              if (row >= lo && row < hi)
+                v = *reinterpret_cast<const uint4*>((h ? xsrc1 : xsrc0) + (size_t)ws.col0 * 128 +
+                                                    (size_t)rem * 16);
+              *reinterpret_cast<uint4*>(my_win + (size_t)idx * 16) = v;
             }
           }
           fence_proxy_async();
+          tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(smem_u32(&bar_a_ready[ab]));
-          pa ^= 1;
-          if (++sd == p.delta_stages) { sd = 0; pd ^= 1; }
+          mbar_arrive(smem_u32(&bar_a_ready[buf]));
         }
       }
 
       // ---------------- epilogue of this fragment ----------------
-      mbar_wait(smem_u32(bar_acc_full), pacc, abort_flag, p.status);
+      mbar_wait_t<INSTR>(smem_u32(bar_acc_full), pacc, abort_flag, p.status, t_accf);
       pacc ^= 1;
       tc_fence_after();
       const bool full_tile = (ku0 == 0 && ku1 == KU);
@@ -598,7 +753,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const int cc = c_first + f;
               const int cu0 = (int)((long long)cc * U / p.grid);
               const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
-              const float* src = p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)cb * 128 + r;
+              const float* src =
+                  p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)cb * 128 + r;
 #pragma unroll
               for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + i * 128);
             }
@@ -617,6 +773,14 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       cta_first_fragment = false;
       u += ku1 - ku0;
+    }
+    if ((p.debug & 16) && ep_tid == 0) {
+      unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
+      atomicAdd(st + 4, (unsigned long long)(clock64() - t_start));
+      atomicAdd(st + 5, (unsigned long long)t_rfull);
+      atomicAdd(st + 6, (unsigned long long)t_afree);
+      atomicAdd(st + 7, (unsigned long long)t_xfull);
+      atomicAdd(st + 8, (unsigned long long)t_accf);
     }
   }
 
@@ -702,7 +866,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
   static thread_local MapEntry* cache = nullptr;
   if (!cache) cache = new MapEntry[kEntries]();
   const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
-  MapEntry& e = cache[(h >> 40) % kEntries ^ (box_rows & 7)];
+  MapEntry& e = cache[((h >> 40) ^ (uintptr_t)box_rows) % kEntries];
   if (e.key.ptr == ptr && e.key.rows == rows && e.key.K == K && e.key.box == box_rows) {
     *map = e.map;
     return DZ_OK;
@@ -761,12 +925,8 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     xsrc = xs;
   }
 
-  CUtensorMap map_w, map_x, map_x32, map_xc;
+  CUtensorMap map_w, map_xc;
   int rc = make_map(&map_w, a.w_base, a.N, a.K, 128);
-  if (rc) return rc;
-  rc = make_map(&map_x, xsrc, a.M, a.K, 16);
-  if (rc) return rc;
-  rc = make_map(&map_x32, xsrc, a.M, a.K, 32);
   if (rc) return rc;
 
   Params p;
@@ -796,18 +956,25 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     p.row0 = tb * kTokenBlock;
     p.cols = min(kTokenBlock, round_up(a.M - p.row0, 16));
     p.xb_bytes = p.cols * 128;
-    p.base_stages = max(2, min(4, kBaseRingBytes / (kATile + p.xb_bytes)));
-    p.delta_stages = p.cols <= 64 ? 5 : (p.cols <= 128 ? 4 : 3);
+    // ring depths: x half-tiles (>= 3, two belong to the unit in flight), W tiles, packed stages
+    p.x_stages = p.cols <= 64 ? 4 : 3;
+    p.w_stages = p.cols <= 128 ? 3 : 2;
+    p.dcols = p.cols <= 128 ? 128 : 256;
+    p.nbuf = p.cols <= 128 ? 8 : 4;
+    const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + p.nbuf * kWinBytes;
+    // packed-stage ring: a multiple of the warpgroup count (slot ownership, see the kernel)
+    p.r_stages = min(kMaxR, (kSmemBudget - fixed) / kRStage) / kNumWG * kNumWG;
+    if (p.r_stages < kNumWG || p.nbuf % kNumWG != 0) return DZ_ERR_UNSUPPORTED;
     rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols);
     if (rc) return rc;
-    const size_t smem = (size_t)p.base_stages * (kATile + p.xb_bytes) +
-                        (size_t)p.delta_stages * kDeltaStageBytes + (size_t)kNumABuf * kATile + 1024;
-    auto kern = (a.bits == 2) ? sbmm_tc_kernel<2> : sbmm_tc_kernel<4>;
-    if (!di.attr_set[bits_idx]) {
-      DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024));
+    const size_t smem = (size_t)fixed + (size_t)p.r_stages * kRStage + 1024;
+    auto kern = (p.debug & 16) ? ((a.bits == 2) ? sbmm_tc_kernel<2, true> : sbmm_tc_kernel<4, true>)
+                               : ((a.bits == 2) ? sbmm_tc_kernel<2, false> : sbmm_tc_kernel<4, false>);
+    if (!di.attr_set[bits_idx] || (p.debug & 16)) {
+      DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
       di.attr_set[bits_idx] = true;
     }
-    kern<<<p.grid, kThreads, smem, st>>>(map_w, map_x, map_x32, map_xc, p);
+    kern<<<p.grid, kThreads, smem, st>>>(map_w, map_xc, p);
     DZ_CUDA_OK(cudaGetLastError());
   }
   return DZ_OK;
