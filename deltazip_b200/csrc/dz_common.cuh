@@ -71,7 +71,7 @@ __host__ __device__ inline size_t meta_offset(int n, int kb, int num_kb, int c, 
 // MMA for that slot runs over the window's columns with rows outside
 // [lo, hi) zeroed.
 // ---------------------------------------------------------------------------
-constexpr int kTokenBlock = 256;
+constexpr int kTokenBlock = 128;
 constexpr int kMaxWindowCols = 32;
 constexpr int kMaxSlots = 4096;
 

@@ -1,12 +1,13 @@
-// The SBMM hot path for sm_100a:  y = x W^T + x dequant(delta_slot)^T, fused in one
-// tensor-memory accumulator.
+// The SBMM hot path for sm_100a:  y = x W^T + x dequant(delta_slot)^T, base and
+// delta products accumulated side by side in tensor memory and added in the
+// epilogue -- no dense delta and no separate add kernel ever exist.
 //
 // Operand roles.  The 128 output features of a tile are the MMA's M dimension
-// (TMEM lanes), the tokens of a token block (<= 256, sorted by slot) are its N
+// (TMEM lanes), the tokens of a token block (<= 128, sorted by slot) are its N
 // dimension (TMEM columns), so a decode batch never pads M up to 128 and every
 // weight byte is streamed from HBM exactly once.
 //   base  : A = W tile [128 x 64] fp16 (TMA, 128B swizzle), B = x half-tile
-//           [cols x 64] (TMA), dense tcgen05.mma (SS), N = cols.
+//           [cols x 64] (TMA), dense tcgen05.mma (SS), N = cols, into D_base.
 //   delta : the packed codes and 2:4 metadata of (slot, tile, k-unit) arrive by
 //           bulk copy; a warpgroup expands the codes to the *compressed* fp16 A
 //           operand directly into tensor memory (one row per thread, one logic
@@ -14,13 +15,18 @@
 //           the metadata next to it, and copies the slot's token window out of
 //           the resident x tile with the rows of other slots zeroed;
 //           tcgen05.mma.sp (A and metadata in TMEM, B in shared memory) then
-//           accumulates into the window's columns of the SAME accumulator the
-//           base product used.
+//           accumulates into the window's columns of D_delta.
 //
-// Shared memory holds four rings sized for what feeds them: W tiles and packed
-// delta stages come from HBM and are kept deep, x half-tiles come from L2 and
-// stay resident for the whole k-unit so that every window is cut from them
-// without another load.
+// Issue parallelism.  One thread can issue a tcgen05.mma only every ~150-200
+// cycles whatever its size, and a decode batch makes many small MMAs (N = 16 or
+// 32 tokens per slot).  The windows of a token block are therefore dealt to C
+// "classes" (window w -> class w mod C), each with its own expansion
+// warpgroup, its own MMA-issuing thread, two expanded-A buffers and its own
+// sub-ring of packed stages; a further thread issues the base MMAs.  A column
+// of D_delta receives non-zero products from one window only (the rows of all
+// other windows over that column are zero), and that window always belongs to
+// the same class, so the summation order of every output is fixed no matter how
+// the issuers interleave.
 //
 // Work split.  (tile, k-unit of 128) pairs are divided evenly over one CTA per
 // SM ("stream-K"): a CTA walks a contiguous unit range, which may cover the
@@ -29,13 +35,11 @@
 // fragment of a tile to finish (a per-tile counter) adds the partials in fixed
 // order, so results do not depend on timing.
 //
-// Warp roles: warp 0 = TMA producer for W and x, warp 1 = MMA issuer and TMEM
-// owner, warp 2 = bulk-copy producer for packed delta stages, warp 3 idle, then
-// four warpgroups of 128 threads that expand codes (delta stage s goes to
-// warpgroup s mod 4) and share the epilogue by column chunks.
 // Every mbarrier wait is bounded: on a timeout the CTA records DZ_ERR_TIMEOUT,
 // raises an abort flag that turns every later wait into a no-op, runs its
-// (bounded) loops to the end and frees its tensor memory.
+// (bounded) loops to the end and frees its tensor memory.  Each barrier has a
+// single, in-order waiter per phase sequence (a parity wait cannot tell phase n
+// from phase n + 2).
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -47,24 +51,30 @@ namespace dz {
 
 namespace {
 
-constexpr int kNumWG = 4;                      // code-expansion warpgroups (128 threads each)
-constexpr int kFirstWGWarp = 4;
+constexpr int kNumWG = 4;                      // warpgroups (128 threads each)
+constexpr int kWarpWX = 0;                     // TMA producer: W tiles, x half-tiles
+constexpr int kWarpBase = 1;                   // base MMA issuer, TMEM owner
+constexpr int kWarpR = 2;                      // bulk-copy producer: packed delta stages
+constexpr int kWarpIssuer0 = 4;                // delta MMA issuers: warps 4..7
+constexpr int kFirstWGWarp = 8;
 constexpr int kThreads = 32 * kFirstWGWarp + 128 * kNumWG;
 constexpr int kUnitK = 128;                    // dense k per work unit
 constexpr int kWTile = 128 * 128;              // bytes: 128 rows x 128 B
 constexpr int kRawBytes = 4096;                // codes of one unit (4-bit)
 constexpr int kMetaBytes = 2048;               // metadata of one unit
 constexpr int kRStage = kRawBytes + kMetaBytes;
-constexpr int kWinBytes = 2 * kMaxWindowCols * 128;   // per-warpgroup window buffer
-constexpr int kMaxW = 4, kMaxX = 8, kMaxR = 16;
-constexpr int kMaxWin = 256;                   // windows of one token block
+constexpr int kWinBytes = 2 * kMaxWindowCols * 128;   // window buffer (B operand of one stage)
+constexpr int kMaxW = 4, kMaxX = 4, kMaxR = 16, kMaxBuf = 8;
+constexpr int kMaxWin = 128;                   // windows of one token block
 constexpr int kTmemCols = 512;
-constexpr int kMaxBuf = 8;                     // expanded-A / metadata / window buffers in flight
-// TMEM columns: accumulator [0, dcols), then 32 columns of expanded A per buffer,
-// then 4 columns of metadata per buffer (dcols = 128 -> 8 buffers, 256 -> 4).
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
 constexpr int kMaxCtas = 160;
 constexpr int kSmemBudget = 216 * 1024;
+
+// TMEM columns: D_base [0, dcols), D_delta [dcols, 2 dcols), then 32 columns of
+// expanded A per buffer, then 4 columns of metadata per buffer.
+//   dcols = 64  : 4 classes, 8 buffers -> 128 + 256 + 32 = 416 columns
+//   dcols = 128 : 3 classes, 6 buffers -> 256 + 192 + 24 = 472 columns
 
 struct Params {
   int M, N, K, bits;
@@ -73,8 +83,8 @@ struct Params {
   int base_only, tokens_sorted;
   int debug;
   int grid, total_units;
-  int w_stages, x_stages, r_stages, xb_bytes;
-  int nbuf, dcols;
+  int w_stages, x_stages, r_per_class, xb_bytes;
+  int nclass, dcols;
   const uint8_t* qweight;
   const uint8_t* meta;
   const uint8_t* scales;
@@ -118,9 +128,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns at once when the CTA is aborting.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
+// Bounded wait (slow path).  Returns at once when the CTA is aborting.
+__device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int* status) {
   if (*abort_flag) return;
   unsigned long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
@@ -138,8 +148,12 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
-// Wait with an inlined first probe; with INSTR the cycles spent are accounted
-// (experiments only).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  if (mbar_try_wait(bar, parity)) return;
+  mbar_wait_slow(bar, parity, abort_flag, status);
+}
+// wait + cycle accounting (experiments only)
 template <bool INSTR>
 __device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int* status, long long& acc) {
@@ -148,7 +162,6 @@ __device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volat
     mbar_wait(bar, parity, abort_flag, status);
     acc += clock64() - t0;
   } else {
-    if (mbar_try_wait(bar, parity)) return;
     mbar_wait(bar, parity, abort_flag, status);
   }
 }
@@ -177,40 +190,14 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B
-// apart, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-  uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
-  d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset
-  d |= (uint64_t)1 << 46;             // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;             // SWIZZLE_128B
-  return d;
-}
 // Instruction descriptor, kind::f16: fp16 A/B (K-major), fp32 accumulate, M = 128.
 __device__ __forceinline__ uint32_t make_idesc(int n, bool sparse) {
   return (sparse ? (1u << 2) : 0u) | (1u << 4) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(128 >> 4) << 24);
 }
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                        uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// 2:4-sparse MMA, compressed A and its metadata both in tensor memory
-__device__ __forceinline__ void umma_ts_sp(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
-                                           uint32_t e_tmem, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], [%1], %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Descriptors are handled as (lo, hi) 32-bit halves: hi is the same for every
-// K-major 128B-swizzled tile, lo carries the start address.
+// Shared-memory matrix descriptors (K-major tile, 128-byte swizzle, rows 128 B
+// apart, 8-row groups 1024 B apart) are handled as (lo, hi) 32-bit halves: hi
+// is the same for every such tile, lo carries the start address.
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) {
   return ((saddr >> 4) & 0x3FFFu) | (1u << 16);
@@ -284,6 +271,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
         "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
@@ -292,6 +281,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
       "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
       "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16_zero(uint32_t taddr) {
+  const uint32_t z = 0;
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
+      "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c,
@@ -369,6 +366,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int C = p.nclass;
+  const int nbuf = 2 * C;
 
   // ---- shared memory carve-up (1024-byte aligned regions) ----
   const uint32_t dyn0 = smem_u32(smem_dyn);
@@ -377,7 +376,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t s_wring = sbase;
   const uint32_t off_x = p.w_stages * kWTile;
   const uint32_t off_win = off_x + p.x_stages * p.xb_bytes;
-  const uint32_t off_r = off_win + p.nbuf * kWinBytes;
+  const uint32_t off_r = off_win + nbuf * kWinBytes;
   const uint32_t s_xring = sbase + off_x;
   const uint32_t s_winbuf = sbase + off_win;
   const uint32_t s_rring = sbase + off_r;
@@ -403,7 +402,9 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     for (int i = 0; i < kMaxX; ++i) {
       mbar_init(smem_u32(&bar_x_full[i]), 1);
-      mbar_init(smem_u32(&bar_x_empty[i]), 1);
+      // freed by the base issuer's commit and, when there are windows, by every
+      // thread of every active expansion warpgroup
+      mbar_init(smem_u32(&bar_x_empty[i]), 1 + (nwin > 0 ? 128 * C : 0));
     }
     for (int i = 0; i < kMaxR; ++i) {
       mbar_init(smem_u32(&bar_r_full[i]), 1);
@@ -413,7 +414,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(smem_u32(&bar_a_ready[i]), 128);
       mbar_init(smem_u32(&bar_a_free[i]), 1);
     }
-    mbar_init(smem_u32(bar_acc_full), 1);
+    mbar_init(smem_u32(bar_acc_full), 1 + (nwin > 0 ? C : 0));
     mbar_init(smem_u32(bar_acc_empty), 128 * kNumWG);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -421,7 +422,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xc) : "memory");
   }
-  if (warp == 1) {
+  if (warp == kWarpBase) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
                  "n"(kTmemCols)
@@ -442,6 +443,16 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
+  // D_delta starts at zero (the delta MMAs always accumulate)
+  if (warp >= kFirstWGWarp && nwin > 0) {
+    const int wg = (warp - kFirstWGWarp) >> 2;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    for (int c = wg; c < p.cols / 16; c += kNumWG) tmem_st16_zero(lane_addr + p.dcols + c * 16);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   // ---- this CTA's unit range ----
   const int cta = blockIdx.x;
@@ -449,13 +460,13 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int u_begin = (int)((long long)cta * U / p.grid);
   const int u_end = (int)((long long)(cta + 1) * U / p.grid);
   const int KU = p.num_kunits;
+  const uint32_t a_col0 = 2 * p.dcols;          // TMEM column of expanded-A buffer 0
+  const uint32_t e_col0 = a_col0 + nbuf * 32;   // TMEM column of metadata buffer 0
 
-  if (warp == 0) {
+  if (warp == kWarpWX) {
     // ====================== TMA producer: W tiles and x half-tiles ======================
     if (lane == 0) {
       Ring rw(p.w_stages, 1), rx(p.x_stages, 1);
-      long long t_w = 0;
-      const long long t_start = clock64();
       for (int u = u_begin; u < u_end;) {
         const int tile = u / KU, ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
@@ -464,12 +475,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const int k0 = ku * kUnitK;
           const int nhalf = min(2, (p.K - k0) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
-            mbar_wait_t<INSTR>(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status, t_w);
+            mbar_wait(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status);
             const uint32_t xfull = smem_u32(&bar_x_full[rx.idx]);
             mbar_expect_tx(xfull, p.xb_bytes);
             tma_load_2d(s_xring + rx.idx * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
             rx.advance();
-            mbar_wait_t<INSTR>(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status, t_w);
+            mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
             const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
             mbar_expect_tx(wfull, kWTile);
             tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
@@ -478,18 +489,19 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         u += ku1 - ku0;
       }
-      if (p.debug & 16) {
-        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
-        atomicAdd(st + 11, (unsigned long long)(clock64() - t_start));
-        atomicAdd(st + 12, (unsigned long long)t_w);
-      }
     }
-  } else if (warp == 2) {
+  } else if (warp == kWarpR) {
     // ====================== bulk-copy producer: packed delta stages ======================
-    if (lane == 0 && nwin > 0) {
-      Ring rr(p.r_stages, 1);
-      long long t_w = 0;
-      const long long t_start = clock64();
+    // class t = w mod C owns sub-ring t (r_per_class slots); its n-th stage uses
+    // slot n mod r_per_class
+    // lane t handles class t: the lanes run the same loop in lock step, so one
+    // warp instruction issues the copies of up to C stages
+    if (lane < C && nwin > 0) {
+      const int t = lane;
+      const int cnt_t = (nwin - t + C - 1) / C;
+      const int cnt_max = (nwin + C - 1) / C;
+      int rs = 0;
+      uint32_t par = 1;
       for (int u = u_begin; u < u_end;) {
         const int tile = u / KU, ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
@@ -498,36 +510,31 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint32_t code_bytes = nhalf * codes_block_bytes(BITS);
           const uint32_t meta_bytes = nhalf * kMetaBlockBytes;
           const size_t blk = (size_t)tile * p.num_kblocks + (size_t)ku * 2;
-          for (int w = 0; w < nwin; ++w) {
-            const int slot = s_win[w].slot;
-            mbar_wait_t<INSTR>(smem_u32(&bar_r_empty[rr.idx]), rr.par, abort_flag, p.status, t_w);
-            const uint32_t full = smem_u32(&bar_r_full[rr.idx]);
-            mbar_expect_tx(full, code_bytes + meta_bytes);
-            const uint32_t dst = s_rring + rr.idx * kRStage;
-            bulk_load(dst, p.qweight + (size_t)slot * p.qstride + blk * codes_block_bytes(BITS),
-                      code_bytes, full);
-            bulk_load(dst + kRawBytes, p.meta + (size_t)slot * p.mstride + blk * kMetaBlockBytes,
-                      meta_bytes, full);
-            rr.advance();
+          for (int j = 0; j < cnt_max; ++j) {
+            if (j < cnt_t) {
+              const int slot_idx = t * p.r_per_class + rs;
+              const int slot = s_win[t + j * C].slot;
+              mbar_wait(smem_u32(&bar_r_empty[slot_idx]), par, abort_flag, p.status);
+              const uint32_t full = smem_u32(&bar_r_full[slot_idx]);
+              mbar_expect_tx(full, code_bytes + meta_bytes);
+              const uint32_t dst = s_rring + slot_idx * kRStage;
+              bulk_load(dst, p.qweight + (size_t)slot * p.qstride + blk * codes_block_bytes(BITS),
+                        code_bytes, full);
+              bulk_load(dst + kRawBytes,
+                        p.meta + (size_t)slot * p.mstride + blk * kMetaBlockBytes, meta_bytes, full);
+              if (++rs == p.r_per_class) { rs = 0; par ^= 1; }
+            }
           }
         }
         u += ku1 - ku0;
       }
-      if (p.debug & 16) {
-        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
-        atomicAdd(st + 9, (unsigned long long)(clock64() - t_start));
-        atomicAdd(st + 10, (unsigned long long)t_w);
-      }
     }
-  } else if (warp == 1) {
-    // =========================== MMA issuer ===========================
+  } else if (warp == kWarpBase) {
+    // =========================== base MMA issuer ===========================
     if (lane == 0) {
       Ring rw(p.w_stages, 0), rx(p.x_stages, 0);
-      uint32_t pa_bits = 0;   // bit b: parity of buffer b's "ready" barrier
-      const uint32_t a_col0 = tmem_base + p.dcols;
-      const uint32_t e_col0 = a_col0 + p.nbuf * 32;
-      int pacc = 1, seq = 0;
-      long long t_acc = 0, t_base = 0, t_ready = 0;
+      int pacc = 1;
+      long long t_acc = 0, t_full = 0;
       const long long t_start = clock64();
       const uint32_t idesc_base = make_idesc(p.cols, false);
       for (int u = u_begin; u < u_end;) {
@@ -538,123 +545,147 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         uint32_t acc = 0;
         for (int ku = ku0; ku < ku1; ++ku) {
-          const int k0 = ku * kUnitK;
-          const int nhalf = min(2, (p.K - k0) / kBlockK);
-          int xslot0 = 0, xslot1 = 0;
+          const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
-            mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_base);
-            mbar_wait_t<INSTR>(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status, t_base);
+            mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_full);
+            mbar_wait_t<INSTR>(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status, t_full);
             tc_fence_after();
-            if (h == 0) xslot0 = rx.idx; else xslot1 = rx.idx;
             umma_ss_x4(tmem_base, desc_lo(s_wring + rw.idx * kWTile),
                        desc_lo(s_xring + rx.idx * p.xb_bytes), idesc_base, acc);
             acc = 1;
             umma_commit(smem_u32(&bar_w_empty[rw.idx]));
+            umma_commit(smem_u32(&bar_x_empty[rx.idx]));
             rw.advance();
             rx.advance();
           }
-          for (int w = 0; w < nwin; ++w) {
-            const WinS ws = s_win[w];
-            const int g = seq % p.nbuf;
-            ++seq;
-            mbar_wait_t<INSTR>(smem_u32(&bar_a_ready[g]), (pa_bits >> g) & 1u, abort_flag, p.status, t_ready);
-            pa_bits ^= 1u << g;
-            tc_fence_after();
-            const uint32_t win_lo = desc_lo(s_winbuf + g * kWinBytes);
-            const uint32_t idesc = make_idesc(ws.ncols, true);
-            const uint32_t dcol = tmem_base + ws.col0;
-            const uint32_t acol = a_col0 + g * 32;
-            const uint32_t ecol = e_col0 + g * 4;
-            if (!(p.debug & 4)) {
-              umma_ts_sp_x2(dcol, acol, win_lo, ecol, idesc);
-              if (nhalf == 2) umma_ts_sp_x2(dcol, acol + 16, win_lo + ws.ncols * 8, ecol + 2, idesc);
-            }
-            umma_commit(smem_u32(&bar_a_free[g]));
-          }
-          // the unit's x half-tiles are free once every MMA above has read them
-          umma_commit(smem_u32(&bar_x_empty[xslot0]));
-          if (nhalf == 2) umma_commit(smem_u32(&bar_x_empty[xslot1]));
         }
         umma_commit(smem_u32(bar_acc_full));
         u += ku1 - ku0;
       }
-      if (p.debug & 16) {
+      if (INSTR) {
         unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
         atomicAdd(st + 0, (unsigned long long)(clock64() - t_start));
         atomicAdd(st + 1, (unsigned long long)t_acc);
-        atomicAdd(st + 2, (unsigned long long)t_base);
-        atomicAdd(st + 3, (unsigned long long)t_ready);
+        atomicAdd(st + 2, (unsigned long long)t_full);
+      }
+    }
+  } else if (warp >= kWarpIssuer0 && warp < kWarpIssuer0 + 4) {
+    // =========================== delta MMA issuer of class t ===========================
+    const int t = warp - kWarpIssuer0;
+    if (lane == 0 && t < C && nwin > 0) {
+      const int cnt_t = (nwin - t + C - 1) / C;
+      int pacc = 1, n = 0;
+      long long t_acc = 0, t_ready = 0;
+      const long long t_start = clock64();
+      for (int u = u_begin; u < u_end;) {
+        const int ku0 = u % KU;
+        const int ku1 = min(KU, ku0 + (u_end - u));
+        mbar_wait_t<INSTR>(smem_u32(bar_acc_empty), pacc, abort_flag, p.status, t_acc);
+        pacc ^= 1;
+        tc_fence_after();
+        for (int ku = ku0; ku < ku1; ++ku) {
+          const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
+          for (int j = 0; j < cnt_t; ++j, ++n) {
+            const WinS ws = s_win[t + j * C];
+            const int buf = t + C * (n & 1);
+            mbar_wait_t<INSTR>(smem_u32(&bar_a_ready[buf]), (n >> 1) & 1, abort_flag, p.status,
+                               t_ready);
+            tc_fence_after();
+            const uint32_t win_lo = desc_lo(s_winbuf + buf * kWinBytes);
+            const uint32_t idesc = make_idesc(ws.ncols, true);
+            const uint32_t dcol = tmem_base + p.dcols + ws.col0;
+            const uint32_t acol = tmem_base + a_col0 + buf * 32;
+            const uint32_t ecol = tmem_base + e_col0 + buf * 4;
+            umma_ts_sp_x2(dcol, acol, win_lo, ecol, idesc);
+            if (nhalf == 2) umma_ts_sp_x2(dcol, acol + 16, win_lo + ws.ncols * 8, ecol + 2, idesc);
+            umma_commit(smem_u32(&bar_a_free[buf]));
+          }
+        }
+        umma_commit(smem_u32(bar_acc_full));
+        u += ku1 - ku0;
+      }
+      if (INSTR && t == 0) {
+        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
+        atomicAdd(st + 3, (unsigned long long)(clock64() - t_start));
+        atomicAdd(st + 4, (unsigned long long)t_acc);
+        atomicAdd(st + 5, (unsigned long long)t_ready);
       }
     }
   } else if (warp >= kFirstWGWarp) {
-    // ================= code expansion + epilogue =================
+    // ================= code expansion (class = warpgroup) + epilogue =================
     const int q = warp & 3;              // TMEM lane quarter this warp may touch
     const int r = q * 32 + lane;         // tile row == TMEM lane
     const int wg = (warp - kFirstWGWarp) >> 2;
     const int wg_tid = (threadIdx.x - 32 * kFirstWGWarp) & 127;
     const int ep_tid = threadIdx.x - 32 * kFirstWGWarp;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    Ring rr(p.r_stages, 0), rx(p.x_stages, 0);
-    uint32_t pa_bits = 0xFFu;   // bit b: parity of buffer b's "free" barrier
-    int pacc = 0, seq = 0;
-    const uint32_t a_col0 = lane_addr + p.dcols;
-    const uint32_t e_col0 = a_col0 + p.nbuf * 32;
+    const bool active = (wg < C) && nwin > 0;
+    const int cnt_t = active ? (nwin - wg + C - 1) / C : 0;
+    Ring rx(p.x_stages, 0);
+    int pacc = 0, n = 0, rs = 0;
+    uint32_t rpar = 0;
     bool cta_first_fragment = true;
+    long long t_deq = 0, t_copy = 0, t_sync = 0;
     long long t_rfull = 0, t_afree = 0, t_xfull = 0, t_accf = 0;
     const long long t_start = clock64();
     const __half2 kBias = __half2half2(__ushort_as_half((unsigned short)(BITS == 4 ? 0x6408 : 0x6402)));
+
+    // scale of the first stage; later ones are fetched one stage ahead
+    __half sc_next = __ushort_as_half((unsigned short)0);
+    if (cnt_t > 0)
+      sc_next = *reinterpret_cast<const __half*>(p.scales + (size_t)s_win[wg].slot * p.sstride +
+                                                 (size_t)((u_begin / KU) * kTileN + r) * 2);
 
     for (int u = u_begin; u < u_end;) {
       const int tile = u / KU, ku0 = u % KU;
       const int ku1 = min(KU, ku0 + (u_end - u));
       const int n0 = tile * kTileN;
-      for (int ku = ku0; ku < ku1 && nwin > 0; ++ku) {
+      for (int ku = ku0; ku < ku1 && active; ++ku) {
         const int k0 = ku * kUnitK;
         const int nhalf = min(2, (p.K - k0) / kBlockK);
-        // the unit's x half-tiles (every warpgroup observes every phase in order)
+        // the unit's x half-tiles
         const uint8_t* xsrc0 = nullptr;
         const uint8_t* xsrc1 = nullptr;
+        int xslot0 = 0, xslot1 = 0;
         for (int h = 0; h < nhalf; ++h) {
           mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_xfull);
-          if (h == 0) xsrc0 = g_xring + rx.idx * p.xb_bytes; else xsrc1 = g_xring + rx.idx * p.xb_bytes;
+          if (h == 0) { xsrc0 = g_xring + rx.idx * p.xb_bytes; xslot0 = rx.idx; }
+          else { xsrc1 = g_xring + rx.idx * p.xb_bytes; xslot1 = rx.idx; }
           rx.advance();
         }
-        for (int w = 0; w < nwin; ++w) {
-          const int buf = seq % p.nbuf;
-          if ((seq++ % kNumWG) != wg) {  // another warpgroup's stage
-            // The ring sizes are multiples of the warpgroup count, so a ring slot
-            // (and an expanded-A buffer) is only ever used by one warpgroup, which
-            // therefore sees each of its phases in order -- a parity wait cannot
-            // tell phase n from phase n + 2.
-            rr.advance();
-            continue;
+        for (int j = 0; j < cnt_t; ++j, ++n) {
+          const WinS ws = s_win[wg + j * C];
+          const __half2 sc2 = __half2half2(sc_next);
+          {  // fetch the next stage's scale now; it is needed a whole stage later
+            const bool same_unit = (j + 1 < cnt_t);
+            const int nt = (same_unit || ku + 1 < ku1) ? tile : min(tile + 1, p.num_tiles - 1);
+            const int nslot = s_win[same_unit ? wg + (j + 1) * C : wg].slot;
+            sc_next = *reinterpret_cast<const __half*>(p.scales + (size_t)nslot * p.sstride +
+                                                       (size_t)(nt * kTileN + r) * 2);
           }
-          const WinS ws = s_win[w];
-          const __half sc = *reinterpret_cast<const __half*>(p.scales + (size_t)ws.slot * p.sstride +
-                                                             (size_t)(n0 + r) * 2);
-          const __half2 sc2 = __half2half2(sc);
-          mbar_wait_t<INSTR>(smem_u32(&bar_r_full[rr.idx]), rr.par, abort_flag, p.status, t_rfull);
-          mbar_wait_t<INSTR>(smem_u32(&bar_a_free[buf]), (pa_bits >> buf) & 1u, abort_flag, p.status, t_afree);
-          pa_bits ^= 1u << buf;
-          uint8_t* const my_win = g_winbuf + buf * kWinBytes;
+          const int buf = wg + C * (n & 1);
+          const int rslot = wg * p.r_per_class + rs;
+          mbar_wait_t<INSTR>(smem_u32(&bar_r_full[rslot]), rpar, abort_flag, p.status, t_rfull);
+          if (++rs == p.r_per_class) { rs = 0; rpar ^= 1; }
+          mbar_wait_t<INSTR>(smem_u32(&bar_a_free[buf]), ((n >> 1) & 1) ^ 1, abort_flag, p.status,
+                             t_afree);
           tc_fence_after();
-          const uint8_t* raw = g_rring + rr.idx * kRStage;
+          long long tc0 = INSTR ? clock64() : 0;
+          const uint8_t* raw = g_rring + rslot * kRStage;
+          uint8_t* const my_win = g_winbuf + buf * kWinBytes;
           uint32_t mw[4] = {0, 0, 0, 0};
           for (int h = 0; h < nhalf; ++h) {
             uint32_t o[16];
-            if (p.debug & 1) {  // experiment: no code expansion, A := 0 (metadata stays valid)
-#pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = 0;
-            } else if (BITS == 4) {
+            if (BITS == 4) {
               const uint4 cw = *reinterpret_cast<const uint4*>(raw + h * 2048 + r * 16);
               const uint32_t wv[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
               for (int wi = 0; wi < 4; ++wi)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  uint32_t t = extract_pair<0x000f000fu>(wv[wi], 4 * j);
-                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), kBias), sc2);
-                  o[wi * 4 + j] = *reinterpret_cast<uint32_t*>(&hv);
+                for (int jj = 0; jj < 4; ++jj) {
+                  uint32_t tt = extract_pair<0x000f000fu>(wv[wi], 4 * jj);
+                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&tt), kBias), sc2);
+                  o[wi * 4 + jj] = *reinterpret_cast<uint32_t*>(&hv);
                 }
             } else {
               const uint2 cw = *reinterpret_cast<const uint2*>(raw + h * 1024 + r * 8);
@@ -662,27 +693,27 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
               for (int wi = 0; wi < 2; ++wi)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  uint32_t t = extract_pair<0x00030003u>(wv[wi], 2 * j);
-                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), kBias), sc2);
-                  o[wi * 8 + j] = *reinterpret_cast<uint32_t*>(&hv);
+                for (int jj = 0; jj < 8; ++jj) {
+                  uint32_t tt = extract_pair<0x00030003u>(wv[wi], 2 * jj);
+                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&tt), kBias), sc2);
+                  o[wi * 8 + jj] = *reinterpret_cast<uint32_t*>(&hv);
                 }
             }
             // compressed A of this half: 32 fp16 = 16 columns of the row's lane
-            tmem_st16(a_col0 + buf * 32 + h * 16, o);
+            tmem_st16(lane_addr + a_col0 + buf * 32 + h * 16, o);
             const uint2 m2 = *reinterpret_cast<const uint2*>(raw + kRawBytes + h * 1024 + r * 8);
             mw[h * 2] = m2.x;
             mw[h * 2 + 1] = m2.y;
           }
-          tmem_st4(e_col0 + buf * 4, mw[0], mw[1], mw[2], mw[3]);
+          tmem_st4(lane_addr + e_col0 + buf * 4, mw[0], mw[1], mw[2], mw[3]);
           // the packed stage has been consumed
-          mbar_arrive(smem_u32(&bar_r_empty[rr.idx]));
-          rr.advance();
+          mbar_arrive(smem_u32(&bar_r_empty[rslot]));
+          if (INSTR) { const long long tc1 = clock64(); t_deq += tc1 - tc0; tc0 = tc1; }
           // the slot's token window: rows of the resident x half-tiles, other slots' rows zeroed
           {
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
             const int per_half = ws.ncols * 8;           // 16-byte chunks
-            const int total = (p.debug & 2) ? 0 : nhalf * per_half;
+            const int total = nhalf * per_half;
             for (int idx = wg_tid; idx < total; idx += 128) {
               const int h = idx >= per_half ? 1 : 0;
               const int rem = idx - h * per_half;
@@ -694,11 +725,16 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               *reinterpret_cast<uint4*>(my_win + (size_t)idx * 16) = v;
             }
           }
+          if (INSTR) { const long long tc1 = clock64(); t_copy += tc1 - tc0; tc0 = tc1; }
           fence_proxy_async();
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_a_ready[buf]));
+          if (INSTR) t_sync += clock64() - tc0;
         }
+        // this warpgroup no longer reads the unit's x half-tiles
+        mbar_arrive(smem_u32(&bar_x_empty[xslot0]));
+        if (nhalf == 2) mbar_arrive(smem_u32(&bar_x_empty[xslot1]));
       }
 
       // ---------------- epilogue of this fragment ----------------
@@ -709,8 +745,15 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       float* my_partial = p.partials +
                           ((size_t)cta * 2 + (cta_first_fragment ? 0 : 1)) * ((size_t)p.cols * 128);
       for (int c = wg; c < p.cols / 16; c += kNumWG) {
-        uint32_t v[16];
+        uint32_t v[16], d[16];
         tmem_ld16(lane_addr + c * 16, v);
+        if (nwin > 0) tmem_ld16(lane_addr + p.dcols + c * 16, d);
+        tmem_wait_ld();
+        if (nwin > 0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(d[i]));
+          tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
+        }
         if (full_tile) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -726,6 +769,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             __stcg(my_partial + (size_t)(c * 16 + i) * 128 + r, __uint_as_float(v[i]));
         }
       }
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(bar_acc_empty));
 
@@ -774,13 +818,16 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       cta_first_fragment = false;
       u += ku1 - ku0;
     }
-    if ((p.debug & 16) && ep_tid == 0) {
+    if (INSTR && ep_tid == 0) {
       unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
-      atomicAdd(st + 4, (unsigned long long)(clock64() - t_start));
-      atomicAdd(st + 5, (unsigned long long)t_rfull);
-      atomicAdd(st + 6, (unsigned long long)t_afree);
-      atomicAdd(st + 7, (unsigned long long)t_xfull);
-      atomicAdd(st + 8, (unsigned long long)t_accf);
+      atomicAdd(st + 6, (unsigned long long)(clock64() - t_start));
+      atomicAdd(st + 7, (unsigned long long)t_rfull);
+      atomicAdd(st + 8, (unsigned long long)t_afree);
+      atomicAdd(st + 9, (unsigned long long)t_xfull);
+      atomicAdd(st + 10, (unsigned long long)t_accf);
+      atomicAdd(st + 11, (unsigned long long)t_deq);
+      atomicAdd(st + 12, (unsigned long long)t_copy);
+      atomicAdd(st + 13, (unsigned long long)t_sync);
     }
   }
 
@@ -794,7 +841,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == kWarpBase) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "n"(kTmemCols)
@@ -881,7 +928,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
 
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[2] = {false, false};
+  bool attr_set[4] = {false, false, false, false};
 };
 DeviceInfo& device_info(int dev) {
   static DeviceInfo info[64];
@@ -949,30 +996,29 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.counters = reinterpret_cast<int*>(ws + kWsCounters);
   p.partials = reinterpret_cast<float*>(ws + kWsPartials);
 
-  const int bits_idx = (a.bits == 2) ? 0 : 1;
+  const bool instr = (p.debug & 16) != 0;
+  const int kidx = ((a.bits == 2) ? 0 : 1) + (instr ? 2 : 0);
   const int num_tb = (a.M + kTokenBlock - 1) / kTokenBlock;
   for (int tb = 0; tb < num_tb; ++tb) {
     p.token_block = tb;
     p.row0 = tb * kTokenBlock;
     p.cols = min(kTokenBlock, round_up(a.M - p.row0, 16));
     p.xb_bytes = p.cols * 128;
-    // ring depths: x half-tiles (>= 3, two belong to the unit in flight), W tiles, packed stages
+    p.dcols = p.cols <= 64 ? 64 : 128;
+    p.nclass = p.cols <= 64 ? 4 : 3;
     p.x_stages = p.cols <= 64 ? 4 : 3;
-    p.w_stages = p.cols <= 128 ? 3 : 2;
-    p.dcols = p.cols <= 128 ? 128 : 256;
-    p.nbuf = p.cols <= 128 ? 8 : 4;
-    const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + p.nbuf * kWinBytes;
-    // packed-stage ring: a multiple of the warpgroup count (slot ownership, see the kernel)
-    p.r_stages = min(kMaxR, (kSmemBudget - fixed) / kRStage) / kNumWG * kNumWG;
-    if (p.r_stages < kNumWG || p.nbuf % kNumWG != 0) return DZ_ERR_UNSUPPORTED;
+    p.w_stages = 3;
+    const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + 2 * p.nclass * kWinBytes;
+    p.r_per_class = min(4, (kSmemBudget - fixed) / (p.nclass * kRStage));
+    if (p.r_per_class < 2 || p.nclass * p.r_per_class > kMaxR) return DZ_ERR_UNSUPPORTED;
     rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols);
     if (rc) return rc;
-    const size_t smem = (size_t)fixed + (size_t)p.r_stages * kRStage + 1024;
-    auto kern = (p.debug & 16) ? ((a.bits == 2) ? sbmm_tc_kernel<2, true> : sbmm_tc_kernel<4, true>)
-                               : ((a.bits == 2) ? sbmm_tc_kernel<2, false> : sbmm_tc_kernel<4, false>);
-    if (!di.attr_set[bits_idx] || (p.debug & 16)) {
+    const size_t smem = (size_t)fixed + (size_t)p.nclass * p.r_per_class * kRStage + 1024;
+    auto kern = instr ? ((a.bits == 2) ? sbmm_tc_kernel<2, true> : sbmm_tc_kernel<4, true>)
+                      : ((a.bits == 2) ? sbmm_tc_kernel<2, false> : sbmm_tc_kernel<4, false>);
+    if (!di.attr_set[kidx]) {
       DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-      di.attr_set[bits_idx] = true;
+      di.attr_set[kidx] = true;
     }
     kern<<<p.grid, kThreads, smem, st>>>(map_w, map_xc, p);
     DZ_CUDA_OK(cudaGetLastError());

@@ -6,7 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def expected_windows(idx, num_slots, token_block=256, max_cols=32):
+def expected_windows(idx, num_slots, token_block=128, max_cols=32):
     idx = np.where((idx >= num_slots) | (idx < -1), -1, idx)
     order = np.sort(idx, kind="stable")
     wins = []
@@ -40,7 +40,7 @@ def test_segment_table(m, slots, sort, seed):
     hdr = seg.header()
     order, wins = expected_windows(idx, slots)
     is_sorted = bool((np.diff(idx) >= 0).all())
-    assert hdr[0] == m and hdr[1] == slots and hdr[2] == (m + 255) // 256
+    assert hdr[0] == m and hdr[1] == slots and hdr[2] == (m + 127) // 128
     assert hdr[3] == int(is_sorted) and hdr[4] == 0
     assert hdr[5] == len(wins) and hdr[6] == len(set(idx[idx >= 0].tolist()))
     raw = seg.buf.cpu().numpy()
@@ -52,12 +52,12 @@ def test_segment_table(m, slots, sort, seed):
     np.testing.assert_array_equal(idx[perm], order)
     if is_sorted:
         np.testing.assert_array_equal(perm, np.arange(m))
-    nb = (m + 255) // 256
+    nb = (m + 127) // 128
     off = 64 + 8 * mr
     bb = raw[off:off + 4 * ((nb + 2 + 15) // 16 * 16)].view(np.int32)
     off += 4 * ((nb + 2 + 15) // 16 * 16)
     w = raw[off:off + 32 * len(wins)].view(np.int32).reshape(-1, 8)[:, :5]
     assert [tuple(r) for r in w.tolist()] == wins
     for tb in range(nb + 1):
-        assert bb[tb] == sum(1 for x in wins if x[1] < tb * 256)
+        assert bb[tb] == sum(1 for x in wins if x[1] < tb * 128)
     assert lib().dz_segments_bytes(m, slots) == seg.buf.numel()
