@@ -347,6 +347,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // ---- early uniform exits (before any barrier or TMEM state exists) ----
   int nwin = 0;
   const int* perm = nullptr;
+  const int* slot_of = nullptr;
   const Window* gwin = nullptr;
   if (p.seg) {
     const SegHeader* hdr = reinterpret_cast<const SegHeader*>(p.seg);
@@ -356,6 +357,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     const SegLayout lay = seg_layout(hdr->capacity_M, hdr->num_slots);
     perm = reinterpret_cast<const int*>(p.seg + lay.perm);
+    slot_of = reinterpret_cast<const int*>(p.seg + lay.slot_of);
     if (!p.base_only) {
       const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
       const int win_begin = bb[p.token_block];
@@ -630,12 +632,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const long long t_start = clock64();
     const __half2 kBias = __half2half2(__ushort_as_half((unsigned short)(BITS == 4 ? 0x6408 : 0x6402)));
 
-    // scale of the first stage; later ones are fetched one stage ahead
-    __half sc_next = __ushort_as_half((unsigned short)0);
-    if (cnt_t > 0)
-      sc_next = *reinterpret_cast<const __half*>(p.scales + (size_t)s_win[wg].slot * p.sstride +
-                                                 (size_t)((u_begin / KU) * kTileN + r) * 2);
-
     for (int u = u_begin; u < u_end;) {
       const int tile = u / KU, ku0 = u % KU;
       const int ku1 = min(KU, ku0 + (u_end - u));
@@ -655,14 +651,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         for (int j = 0; j < cnt_t; ++j, ++n) {
           const WinS ws = s_win[wg + j * C];
-          const __half2 sc2 = __half2half2(sc_next);
-          {  // fetch the next stage's scale now; it is needed a whole stage later
-            const bool same_unit = (j + 1 < cnt_t);
-            const int nt = (same_unit || ku + 1 < ku1) ? tile : min(tile + 1, p.num_tiles - 1);
-            const int nslot = s_win[same_unit ? wg + (j + 1) * C : wg].slot;
-            sc_next = *reinterpret_cast<const __half*>(p.scales + (size_t)nslot * p.sstride +
-                                                       (size_t)(nt * kTileN + r) * 2);
-          }
           const int buf = wg + C * (n & 1);
           const int rslot = wg * p.r_per_class + rs;
           mbar_wait_t<INSTR>(smem_u32(&bar_r_full[rslot]), rpar, abort_flag, p.status, t_rfull);
@@ -684,7 +672,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
                   uint32_t tt = extract_pair<0x000f000fu>(wv[wi], 4 * jj);
-                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&tt), kBias), sc2);
+                  __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&tt), kBias);
                   o[wi * 4 + jj] = *reinterpret_cast<uint32_t*>(&hv);
                 }
             } else {
@@ -695,7 +683,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
                   uint32_t tt = extract_pair<0x00030003u>(wv[wi], 2 * jj);
-                  __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&tt), kBias), sc2);
+                  __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&tt), kBias);
                   o[wi * 8 + jj] = *reinterpret_cast<uint32_t*>(&hv);
                 }
             }
@@ -714,14 +702,15 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
             const int per_half = ws.ncols * 8;           // 16-byte chunks
             const int total = nhalf * per_half;
+            const uint8_t* x0 = xsrc0 + (size_t)ws.col0 * 128;
+            const uint8_t* x1 = xsrc1 + (size_t)ws.col0 * 128 - (size_t)per_half * 16;
+#pragma unroll 2
             for (int idx = wg_tid; idx < total; idx += 128) {
-              const int h = idx >= per_half ? 1 : 0;
-              const int rem = idx - h * per_half;
-              const int row = rem >> 3;
+              const bool h = idx >= per_half;
+              const int row = (idx - (h ? per_half : 0)) >> 3;
               uint4 v = make_uint4(0, 0, 0, 0);
               if (row >= lo && row < hi)
-                v = *reinterpret_cast<const uint4*>((h ? xsrc1 : xsrc0) + (size_t)ws.col0 * 128 +
-                                                    (size_t)rem * 16);
+                v = *reinterpret_cast<const uint4*>((h ? x1 : x0) + (size_t)idx * 16);
               *reinterpret_cast<uint4*>(my_win + (size_t)idx * 16) = v;
             }
           }
@@ -738,6 +727,30 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
 
       // ---------------- epilogue of this fragment ----------------
+      // D_delta holds sums of (code - zero) * x; the per-channel scale of each
+      // column's slot is applied here.  The scales do not depend on the
+      // accumulators, so they are fetched before the wait.
+      unsigned short csc[2][16];   // fp16 bit patterns (0 for base-only columns)
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) csc[cc][i] = 0;
+      if (nwin > 0) {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = wg + cc * kNumWG;
+          if (c < p.cols / 16) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int prow = p.row0 + c * 16 + i;
+              const int slot = (prow < p.M) ? slot_of[prow] : -1;
+              if (slot >= 0)
+                csc[cc][i] = *reinterpret_cast<const unsigned short*>(
+                    p.scales + (size_t)slot * p.sstride + (size_t)(n0 + r) * 2);
+            }
+          }
+        }
+      }
       mbar_wait_t<INSTR>(smem_u32(bar_acc_full), pacc, abort_flag, p.status, t_accf);
       pacc ^= 1;
       tc_fence_after();
@@ -750,8 +763,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (nwin > 0) tmem_ld16(lane_addr + p.dcols + c * 16, d);
         tmem_wait_ld();
         if (nwin > 0) {
+          const int cc = (c - wg) / kNumWG;   // 0 or 1 (cols <= 128)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(d[i]));
+          for (int i = 0; i < 16; ++i)
+            v[i] = __float_as_uint(fmaf(__half2float(__ushort_as_half(cc ? csc[1][i] : csc[0][i])),
+                                        __uint_as_float(d[i]), __uint_as_float(v[i])));
           tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
         }
         if (full_tile) {
@@ -778,9 +794,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int c_first = cta_of_unit((long long)tile * KU, p.grid, p.total_units);
         const int c_last = cta_of_unit((long long)(tile + 1) * KU - 1, p.grid, p.total_units);
         const int nfrag = c_last - c_first + 1;
-        __threadfence();
+        // release pattern: every thread's partial stores happen before the
+        // barrier; one thread then fences at device scope and publishes
         named_bar_sync(1, 128 * kNumWG);
         if (ep_tid == 0) {
+          __threadfence();
           const int old = atomicAdd(&p.counters[tile], 1);
           s_last = (old == nfrag - 1) ? 1 : 0;
         }

@@ -126,7 +126,10 @@ class Segments:
                                       self.buf.data_ptr(), _stream()), "dz_build_segments")
         self.m = m
         if sorted_hint is None:
-            sorted_hint = bool(m < 2 or (indices[1:] >= indices[:-1]).all().item())
+            # same clamping as the device builder: ids outside [-1, num_slots) count as -1
+            c = torch.where((indices >= self.num_slots) | (indices < -1),
+                            torch.full_like(indices, -1), indices)
+            sorted_hint = bool(m < 2 or (c[1:] >= c[:-1]).all().item())
         self.sorted = bool(sorted_hint)
         return self
 
