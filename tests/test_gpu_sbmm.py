@@ -125,7 +125,12 @@ def test_linearity_property_full_size():
     seg = ops.Segments(64, 8, "cuda").build(dev(idx))
     y1 = ops.sbmm(dev(x), layer.qweight, layer.scales, layer.meta, seg, layer.w).cpu().numpy()
     y2 = ops.sbmm(dev(x * np.float16(2)), layer.qweight, layer.scales, layer.meta, seg, layer.w).cpu().numpy()
-    np.testing.assert_array_equal((y1 * np.float16(2)).view(np.uint16), y2.view(np.uint16))
+    # exact wherever the result is a normal fp16 number (a subnormal result has
+    # fewer significant bits than its double, so rounding may differ there)
+    normal = np.abs(y1.astype(np.float32)) >= 2.0 ** -13
+    assert normal.mean() > 0.999
+    np.testing.assert_array_equal((y1 * np.float16(2)).view(np.uint16)[normal],
+                                  y2.view(np.uint16)[normal])
     np.testing.assert_array_equal(y1[0].view(np.uint16), y1[1].view(np.uint16))
     # spot-check 4 rows against the oracle at full size
     rows = [0, 17, 40, 63]
