@@ -137,6 +137,21 @@ typedef struct {
 size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted);
 int dz_sbmm(const dz_sbmm_args* args, void* stream);
 
+/*
+ * dz_sbmm for callers that cannot allocate device memory (no counterpart in the
+ * reference, which allocates freely through PyTorch).  Same arguments and
+ * results as dz_sbmm, but `workspace` / `workspace_bytes` are ignored: the
+ * scratch lives in a fixed array inside the library, so the call makes no
+ * cudaMalloc / cudaFree and calls no allocating routine.  Limits: M <=
+ * dz_sbmm_static_max_tokens() (64) and tokens_sorted must be 1, otherwise
+ * DZ_ERR_TOO_LARGE.  Each GPU that loads the library holds about 10.5 MB for
+ * this array until the process exits.  The first call on a device looks up the
+ * array's device address (make it before any stream capture).  All calls on a
+ * device share the array: calls that overlap on the GPU race -- order them.
+ */
+int dz_sbmm_static(const dz_sbmm_args* args, void* stream);
+int dz_sbmm_static_max_tokens(void);
+
 /* Base GEMM alone, y = x W^T (all tokens -1); same argument block, the slot
  * pointers and `segments` may be NULL.
  * serving/vllm/model_executor/layers/linear.py:85-96 */
