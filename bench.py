@@ -111,7 +111,7 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_model(tp, rank, device, seed=0):
+def build_model(tp, rank, device, seed=0, num_layers=LAYERS):
     """Per layer and projection: base weight, slot stacks.  Deltas are generated and
     compressed once per projection shape and replicated (device copies) per layer."""
     import torch
@@ -123,7 +123,7 @@ def build_model(tp, rank, device, seed=0):
         proto[name] = synth.random_delta_slots(NUM_DELTAS, n, k, BITS, seed=seed + 100 * i + rank,
                                                device=device)
     layers = []
-    for layer in range(LAYERS):
+    for layer in range(num_layers):
         entry = {}
         for name, n, k, rowp in projs:
             w = torch.empty((n, k), dtype=torch.float16, device=device)
@@ -153,7 +153,7 @@ def run_ours(args):
     tp = world
     L = _lib.lib()
 
-    projs, layers = build_model(tp, rank, device)
+    projs, layers = build_model(tp, rank, device, num_layers=args.layers)
     g = torch.Generator(device="cpu").manual_seed(1234)
     idx_host = torch.sort(torch.randint(0, NUM_DELTAS, (TOKENS,), generator=g))[0].to(torch.int64)
     active = len(set(idx_host.tolist()))
@@ -281,11 +281,11 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {
                 "workload": "configs[1]: SBMM over Llama-2-7B projection shapes (qkv 12288x4096, "
-                            "o 4096x4096, gate_up 22016x4096, down 4096x11008) x 32 layers, "
+                            "o 4096x4096, gate_up 22016x4096, down 4096x11008) x %d layers, " % args.layers +
                             "8 deltas 4-bit 2:4 sym per-channel, 64-token decode batch, slot ids "
                             "uniform over 8 (sorted)",
                 "tokens": TOKENS, "deltas": NUM_DELTAS, "active_deltas": active, "bits": BITS,
-                "layers": LAYERS, "sbmm_calls_per_step": n_calls,
+                "layers": args.layers, "sbmm_calls_per_step": n_calls,
                 "parallelism": f"tp{world}",
                 "l2": "inputs larger than L2: each step streams %.1f GB of distinct weights"
                       % (step_bytes * 1e-9),
@@ -306,7 +306,7 @@ def run_ours(args):
             "clocks": clocks,
             "kernel_status": status,
         }
-        if world == 1:
+        if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -429,6 +429,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS,
+                    help="decoder layers to instantiate (32 = the benchmark; fewer only for profiling captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
