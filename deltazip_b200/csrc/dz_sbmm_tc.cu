@@ -55,8 +55,8 @@ constexpr int kNumWG = 4;                      // warpgroups (128 threads each)
 constexpr int kWarpWX = 0;                     // TMA producer: W tiles, x half-tiles
 constexpr int kWarpBase = 1;                   // base MMA issuer, TMEM owner
 constexpr int kWarpR = 2;                      // bulk-copy producer: packed delta stages
-constexpr int kWarpIssuer0 = 4;                // delta MMA issuers: warps 4..7
-constexpr int kFirstWGWarp = 8;
+constexpr int kWarpIssuer0 = 3;                // delta MMA issuers: warps 3..6
+constexpr int kFirstWGWarp = 7;                 // any 4 consecutive warps cover the 4 TMEM lane quarters
 constexpr int kThreads = 32 * kFirstWGWarp + 128 * kNumWG;
 constexpr int kUnitK = 128;                    // dense k per work unit
 constexpr int kWTile = 128 * 128;              // bytes: 128 rows x 128 B
@@ -135,6 +135,7 @@ __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volat
   unsigned long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return;
+    __nanosleep(32);   // keep polling warps out of the issue slots of working ones
     if ((it & 63u) == 63u) {
       if (*abort_flag) return;
       const unsigned long long now = globaltimer();
@@ -304,13 +305,39 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// (v >> shift) & mask | 0x64006400, i.e. the fp16 pair (1024 + code_lo, 1024 + code_hi)
-template <uint32_t MASK>
-__device__ __forceinline__ uint32_t extract_pair(uint32_t w, int shift) {
-  uint32_t r;
-  const uint32_t s = w >> shift;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(s), "n"(MASK), "n"(0x64006400));
-  return r;
+// The fp16 pair (code_lo - zero, code_hi - zero) from the BITS-wide fields at bit P
+// of both half-words of w, without shifting: OR-ing the field into the mantissa
+// of 2^(10-P) gives 2^(10-P) + code (the field has weight 2^-P there), and one
+// subtraction of 2^(10-P) + zero leaves the exact small integer.  P + BITS <= 10.
+template <int BITS, int P>
+__device__ __forceinline__ uint32_t code_pair(uint32_t w) {
+  constexpr uint32_t kMask = ((((1u << BITS) - 1u) << P)) * 0x00010001u;
+  constexpr uint32_t kMagic = ((25u - P) << 10) * 0x00010001u;
+  constexpr uint32_t kBiasBits = (((25u - P) << 10) | ((1u << (BITS - 1)) << P)) * 0x00010001u;
+  uint32_t t;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(w), "n"(kMask), "n"(kMagic));
+  uint32_t b = kBiasBits;
+  __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&hv);
+}
+// the 8 (4-bit) or 16 (2-bit) kept values of one packed word -> 4 / 8 fp16 pairs
+__device__ __forceinline__ void expand_word4(uint32_t w, uint32_t* o) {
+  const uint32_t s = w >> 8;
+  o[0] = code_pair<4, 0>(w);
+  o[1] = code_pair<4, 4>(w);
+  o[2] = code_pair<4, 0>(s);
+  o[3] = code_pair<4, 4>(s);
+}
+__device__ __forceinline__ void expand_word2(uint32_t w, uint32_t* o) {
+  const uint32_t s = w >> 10;
+  o[0] = code_pair<2, 0>(w);
+  o[1] = code_pair<2, 2>(w);
+  o[2] = code_pair<2, 4>(w);
+  o[3] = code_pair<2, 6>(w);
+  o[4] = code_pair<2, 8>(w);
+  o[5] = code_pair<2, 0>(s);
+  o[6] = code_pair<2, 2>(s);
+  o[7] = code_pair<2, 4>(s);
 }
 
 // CTA that owns unit u when `total` units are split evenly over `grid` CTAs
@@ -341,6 +368,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t s_bars[2 * kMaxW + 2 * kMaxX + 2 * kMaxR + 2 * kMaxBuf + 2];
   __shared__ WinS s_win[kMaxWin];
+  __shared__ int s_slot[kTokenBlock];   // slot of each column of the token block (-1: base only)
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_last;
 
@@ -430,6 +458,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                  "n"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < kTokenBlock; i += kThreads) {
+    const int prow = p.row0 + i;
+    s_slot[i] = (slot_of && !p.base_only && prow < p.M) ? slot_of[prow] : -1;
   }
   for (int i = threadIdx.x; i < nwin; i += kThreads) {
     const Window w = gwin[i];
@@ -627,15 +659,31 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int pacc = 0, n = 0, rs = 0;
     uint32_t rpar = 0;
     bool cta_first_fragment = true;
-    long long t_deq = 0, t_copy = 0, t_sync = 0;
+    long long t_deq = 0, t_copy = 0, t_sync = 0, t_epi = 0;
     long long t_rfull = 0, t_afree = 0, t_xfull = 0, t_accf = 0;
     const long long t_start = clock64();
-    const __half2 kBias = __half2half2(__ushort_as_half((unsigned short)(BITS == 4 ? 0x6408 : 0x6402)));
 
     for (int u = u_begin; u < u_end;) {
       const int tile = u / KU, ku0 = u % KU;
       const int ku1 = min(KU, ku0 + (u_end - u));
       const int n0 = tile * kTileN;
+      // D_delta holds sums of (code - zero) * x; the per-channel scale of each
+      // column's slot is applied in the epilogue.  The scales depend only on
+      // (tile, column), so they are fetched now and arrive during the main loop.
+      uint32_t csc[8];   // fp16 bit patterns of column chunk `wg`, two columns per word
+#pragma unroll
+      for (int i = 0; i < 8; ++i) csc[i] = 0;
+      if (nwin > 0 && wg < p.cols / 16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int slot = s_slot[wg * 16 + i];
+          uint32_t v = 0;
+          if (slot >= 0)
+            v = *reinterpret_cast<const unsigned short*>(p.scales + (size_t)slot * p.sstride +
+                                                         (size_t)(n0 + r) * 2);
+          csc[i >> 1] |= v << (16 * (i & 1));
+        }
+      }
       for (int ku = ku0; ku < ku1 && active; ++ku) {
         const int k0 = ku * kUnitK;
         const int nhalf = min(2, (p.K - k0) / kBlockK);
@@ -668,24 +716,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const uint4 cw = *reinterpret_cast<const uint4*>(raw + h * 2048 + r * 16);
               const uint32_t wv[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
-              for (int wi = 0; wi < 4; ++wi)
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                  uint32_t tt = extract_pair<0x000f000fu>(wv[wi], 4 * jj);
-                  __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&tt), kBias);
-                  o[wi * 4 + jj] = *reinterpret_cast<uint32_t*>(&hv);
-                }
+              for (int wi = 0; wi < 4; ++wi) expand_word4(wv[wi], o + wi * 4);
             } else {
               const uint2 cw = *reinterpret_cast<const uint2*>(raw + h * 1024 + r * 8);
               const uint32_t wv[2] = {cw.x, cw.y};
 #pragma unroll
-              for (int wi = 0; wi < 2; ++wi)
-#pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                  uint32_t tt = extract_pair<0x00030003u>(wv[wi], 2 * jj);
-                  __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&tt), kBias);
-                  o[wi * 8 + jj] = *reinterpret_cast<uint32_t*>(&hv);
-                }
+              for (int wi = 0; wi < 2; ++wi) expand_word2(wv[wi], o + wi * 8);
             }
             // compressed A of this half: 32 fp16 = 16 columns of the row's lane
             tmem_st16(lane_addr + a_col0 + buf * 32 + h * 16, o);
@@ -727,30 +763,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
 
       // ---------------- epilogue of this fragment ----------------
-      // D_delta holds sums of (code - zero) * x; the per-channel scale of each
-      // column's slot is applied here.  The scales do not depend on the
-      // accumulators, so they are fetched before the wait.
-      unsigned short csc[2][16];   // fp16 bit patterns (0 for base-only columns)
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) csc[cc][i] = 0;
-      if (nwin > 0) {
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = wg + cc * kNumWG;
-          if (c < p.cols / 16) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int prow = p.row0 + c * 16 + i;
-              const int slot = (prow < p.M) ? slot_of[prow] : -1;
-              if (slot >= 0)
-                csc[cc][i] = *reinterpret_cast<const unsigned short*>(
-                    p.scales + (size_t)slot * p.sstride + (size_t)(n0 + r) * 2);
-            }
-          }
-        }
-      }
+      const long long te0 = INSTR ? clock64() : 0;
+      const long long accf0 = t_accf;
       mbar_wait_t<INSTR>(smem_u32(bar_acc_full), pacc, abort_flag, p.status, t_accf);
       pacc ^= 1;
       tc_fence_after();
@@ -763,11 +777,24 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (nwin > 0) tmem_ld16(lane_addr + p.dcols + c * 16, d);
         tmem_wait_ld();
         if (nwin > 0) {
-          const int cc = (c - wg) / kNumWG;   // 0 or 1 (cols <= 128)
+          if (c != wg) {   // second chunk of a wide token block: its scales are fetched here
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            v[i] = __float_as_uint(fmaf(__half2float(__ushort_as_half(cc ? csc[1][i] : csc[0][i])),
-                                        __uint_as_float(d[i]), __uint_as_float(v[i])));
+            for (int i = 0; i < 8; ++i) csc[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int slot = s_slot[c * 16 + i];
+              uint32_t sv = 0;
+              if (slot >= 0)
+                sv = *reinterpret_cast<const unsigned short*>(p.scales + (size_t)slot * p.sstride +
+                                                              (size_t)(n0 + r) * 2);
+              csc[i >> 1] |= sv << (16 * (i & 1));
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float sc = __half2float(__ushort_as_half((unsigned short)(csc[i >> 1] >> (16 * (i & 1)))));
+            v[i] = __float_as_uint(fmaf(sc, __uint_as_float(d[i]), __uint_as_float(v[i])));
+          }
           tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
         }
         if (full_tile) {
@@ -805,20 +832,35 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         named_bar_sync(1, 128 * kNumWG);
         if (s_last) {
           __threadfence();
-          // 8 columns per pass so that eight independent L2 loads are in flight
-          // per fragment (a column-at-a-time loop is a chain of L2 latencies)
+          // 8 columns x 2 fragments per pass: 16 independent L2 loads in
+          // flight (a column-at-a-time loop is a chain of L2 latencies); the
+          // additions stay in fragment order
           for (int cb = wg * 8; cb < p.cols; cb += kNumWG * 8) {
             float sum[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-            for (int f = 0; f < nfrag; ++f) {
-              const int cc = c_first + f;
-              const int cu0 = (int)((long long)cc * U / p.grid);
-              const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
-              const float* src =
-                  p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)cb * 128 + r;
+            for (int f0 = 0; f0 < nfrag; f0 += 2) {
+              float part[2][8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + i * 128);
+              for (int ff = 0; ff < 2; ++ff) {
+                const int f = f0 + ff;
+                if (f < nfrag) {
+                  const int cc = c_first + f;
+                  const int cu0 = (int)((long long)cc * U / p.grid);
+                  const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
+                  const float* src =
+                      p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)cb * 128 + r;
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) part[ff][i] = __ldcg(src + i * 128);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) part[ff][i] = 0.f;
+                }
+              }
+#pragma unroll
+              for (int ff = 0; ff < 2; ++ff)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] += part[ff][i];
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -835,6 +877,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       cta_first_fragment = false;
       u += ku1 - ku0;
+      if (INSTR) t_epi += (clock64() - te0) - (t_accf - accf0);
     }
     if (INSTR && ep_tid == 0) {
       unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
@@ -846,6 +889,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       atomicAdd(st + 11, (unsigned long long)t_deq);
       atomicAdd(st + 12, (unsigned long long)t_copy);
       atomicAdd(st + 13, (unsigned long long)t_sync);
+      atomicAdd(st + 14, (unsigned long long)t_epi);
     }
   }
 

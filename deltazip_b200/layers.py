@@ -1,0 +1,299 @@
+"""Delta linear layers: the reference's plugin interface over the B200 SBMM.
+
+Same classes, method names and argument meaning as
+serving/vllm/delta/layers_marlin.py:47-611 (`DeltaMapping`, `BaseLayerWithDelta`
+with create_delta_weights / set_delta / reset_delta / set_mapping /
+apply_weights / forward, `from_layer`), so that a model runner written for the
+reference drives them unchanged.  The base parallel linears the reference takes
+from vLLM (serving/vllm/model_executor/layers/linear.py:157-650) are reduced
+here to what the delta layers read from them: the sharded fp16 weight and the
+parallel flags.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .config import DeltaConfig
+from .parallel_state import (get_tensor_model_parallel_rank, get_tensor_model_parallel_world_size,
+                             shard_range, tensor_model_parallel_all_gather,
+                             tensor_model_parallel_all_reduce)
+
+ASYNC_COPY = True
+
+
+@dataclass
+class DeltaMapping:
+    """Per-token and per-sampled-token delta ids of one batch (0 / None = base model)."""
+    index_mapping: Tuple[int, ...]
+    prompt_mapping: Tuple[int, ...]
+
+    def __post_init__(self):
+        self.index_mapping = tuple(self.index_mapping)
+        self.prompt_mapping = tuple(self.prompt_mapping)
+
+
+# ---------------------------------------------------------------------------
+# base layers (what the delta layers need of vLLM's parallel linears)
+# ---------------------------------------------------------------------------
+
+class _ParallelLinearBase(nn.Module):
+    def __init__(self, weight: torch.Tensor):
+        super().__init__()
+        self.weight = nn.Parameter(weight, requires_grad=False)
+        self.bias = None
+        self.skip_bias_add = False
+        self.tp_size = get_tensor_model_parallel_world_size()
+
+    @property
+    def linear_weights(self):
+        return {"weight": self.weight}
+
+
+class ColumnParallelLinear(_ParallelLinearBase):
+    """y = x W^T with W split along the output dimension (whole 128-row tiles per rank)."""
+
+    def __init__(self, input_size: int, output_size: int, full_weight: Optional[torch.Tensor] = None,
+                 gather_output: bool = False, device="cuda", dtype=torch.float16):
+        rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
+        lo, hi = shard_range(output_size, 128, rank, size)
+        if full_weight is None:
+            w = torch.empty((hi - lo, input_size), dtype=dtype, device=device).normal_(0, 0.02)
+        else:
+            w = full_weight[lo:hi].to(device=device, dtype=dtype).contiguous()
+        super().__init__(w)
+        self.input_size, self.output_size = input_size, output_size
+        self.shard = (lo, hi)
+        self.gather_output = gather_output
+
+    def forward(self, x):
+        y = ops.base_gemm(x, self.weight)
+        return (tensor_model_parallel_all_gather(y) if self.gather_output else y), None
+
+
+class MergedColumnParallelLinear(ColumnParallelLinear):
+    """Several equally sharded column-parallel matrices stacked (gate_proj + up_proj)."""
+
+    def __init__(self, input_size: int, output_sizes: List[int],
+                 full_weights: Optional[List[torch.Tensor]] = None, device="cuda",
+                 dtype=torch.float16):
+        rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
+        parts, self.shards = [], []
+        for i, out in enumerate(output_sizes):
+            lo, hi = shard_range(out, 128, rank, size)
+            self.shards.append((lo, hi))
+            if full_weights is None:
+                parts.append(torch.empty((hi - lo, input_size), dtype=dtype, device=device).normal_(0, 0.02))
+            else:
+                parts.append(full_weights[i][lo:hi].to(device=device, dtype=dtype))
+        _ParallelLinearBase.__init__(self, torch.cat(parts, dim=0).contiguous())
+        self.input_size, self.output_sizes = input_size, list(output_sizes)
+        self.output_size = sum(output_sizes)
+        self.gather_output = False
+
+
+class QKVParallelLinear(MergedColumnParallelLinear):
+    """q, k, v projections stacked; heads are split over the ranks."""
+
+    def __init__(self, hidden_size: int, head_size: int, total_num_heads: int,
+                 total_num_kv_heads: Optional[int] = None,
+                 full_weights: Optional[List[torch.Tensor]] = None, device="cuda",
+                 dtype=torch.float16):
+        total_num_kv_heads = total_num_kv_heads or total_num_heads
+        size = get_tensor_model_parallel_world_size()
+        self.head_size = head_size
+        self.num_heads = total_num_heads // size
+        self.num_kv_heads = max(1, total_num_kv_heads // size)
+        super().__init__(hidden_size, [total_num_heads * head_size, total_num_kv_heads * head_size,
+                                       total_num_kv_heads * head_size], full_weights, device, dtype)
+
+
+class RowParallelLinear(_ParallelLinearBase):
+    """y = x W^T with W split along the input dimension (whole 64-column blocks per rank),
+    partial results summed over the ranks."""
+
+    def __init__(self, input_size: int, output_size: int, full_weight: Optional[torch.Tensor] = None,
+                 input_is_parallel: bool = True, reduce_results: bool = True, device="cuda",
+                 dtype=torch.float16):
+        rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
+        lo, hi = shard_range(input_size, 64, rank, size)
+        if full_weight is None:
+            w = torch.empty((output_size, hi - lo), dtype=dtype, device=device).normal_(0, 0.02)
+        else:
+            w = full_weight[:, lo:hi].to(device=device, dtype=dtype).contiguous()
+        super().__init__(w)
+        self.input_size, self.output_size = input_size, output_size
+        self.shard = (lo, hi)
+        self.input_is_parallel = input_is_parallel
+        self.reduce_results = reduce_results
+
+    def forward(self, x):
+        if not self.input_is_parallel:
+            x = x[..., self.shard[0]:self.shard[1]].contiguous()
+        y = ops.base_gemm(x, self.weight)
+        if self.reduce_results and self.tp_size > 1:
+            y = tensor_model_parallel_all_reduce(y)
+        return y, None
+
+
+# ---------------------------------------------------------------------------
+# delta layers
+# ---------------------------------------------------------------------------
+
+class BaseLayerWithDelta(nn.Module):
+    """Owns the stacked slot tensors of one linear layer and applies the SBMM."""
+
+    def __init__(self, base_layer: nn.Module) -> None:
+        super().__init__()
+        self.base_layer = base_layer
+        self.tp_size = get_tensor_model_parallel_world_size()
+        self.tp_rank = get_tensor_model_parallel_rank()
+        self.indices: Optional[torch.Tensor] = None
+        self.indices_len: Optional[List[int]] = None
+        self.segments: Optional[ops.Segments] = None
+        self.bits = 4
+
+    # -- slots ---------------------------------------------------------------
+    def create_delta_weights(self, max_deltas: int, delta_config: DeltaConfig,
+                             model_config=None) -> None:
+        """Allocates zeroed slot stacks: qweight int32 [D, K*b/128, 2N], scales fp16 [D, 1, N],
+        meta int16 [D, N, K/16] for this rank's weight shard [N, K]."""
+        n, k = self.base_layer.weight.shape
+        self.bits = delta_config.max_bitwidth
+        self.pack_factor = delta_config.pack_factor
+        self.bitwidth = [0] * max_deltas
+        self.qweight_stacked, self.meta_stacked, self.scales_stacked = ops.alloc_slots(
+            max_deltas, n, k, self.bits, self.base_layer.weight.device)
+
+    def reset_delta(self, index: int):
+        self.bitwidth[index] = 0
+        self.qweight_stacked[index] = 0
+        self.scales_stacked[index] = 0
+        self.meta_stacked[index] = 0
+
+    def set_delta(self, index: int, bitwidth: int, qweight: torch.Tensor,
+                  qzeros: Optional[torch.Tensor], scales: torch.Tensor,
+                  g_idx: Optional[torch.Tensor] = None, meta: Optional[torch.Tensor] = None):
+        """Overwrites slot `index`.  With `meta` the tensors are already in slot layout and are
+        copied (asynchronously when they are pinned); with `qzeros` they are GPTQ-layout
+        tensors of this rank's shard and are converted on the device."""
+        if bitwidth != self.bits:
+            raise ValueError(f"slot stack holds {self.bits}-bit deltas, got {bitwidth}")
+        self.bitwidth[index] = bitwidth
+        if meta is not None:
+            self.qweight_stacked[index].copy_(qweight, non_blocking=ASYNC_COPY)
+            self.scales_stacked[index].copy_(scales.reshape(self.scales_stacked[index].shape),
+                                             non_blocking=ASYNC_COPY)
+            self.meta_stacked[index].copy_(meta, non_blocking=ASYNC_COPY)
+        else:
+            dev = self.qweight_stacked.device
+            ops.convert_from_gptq(qweight.to(dev, non_blocking=True), qzeros.to(dev, non_blocking=True),
+                                  scales.to(dev, non_blocking=True), bitwidth,
+                                  out=(self.qweight_stacked[index], self.meta_stacked[index],
+                                       self.scales_stacked[index]))
+
+    # -- mapping -------------------------------------------------------------
+    def set_mapping(self, base_indices: torch.Tensor, sampler_indices: torch.Tensor = None,
+                    sampler_indices_padded: torch.Tensor = None,
+                    embeddings_indices: torch.Tensor = None, indices_len: List[int] = None,
+                    segments: Optional[ops.Segments] = None):
+        """Keeps references to the manager's shared index buffers (and its segment table)."""
+        self.indices = base_indices
+        self.indices_len = indices_len
+        self.segments = segments
+
+    # -- compute -------------------------------------------------------------
+    def apply_weights(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if bias is not None:
+            raise ValueError("delta layers do not support bias yet.")
+        w = self.base_layer.linear_weights["weight"]
+        if self.segments is not None:
+            return ops.sbmm(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
+                            self.segments, w, bits=self.bits)
+        return ops.apply_delta(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
+                               self.indices[: self.indices_len[0]], w)
+
+    @property
+    def linear_weights(self):
+        return self.base_layer.linear_weights
+
+    @property
+    def weight(self):
+        return self.base_layer.weight
+
+
+class ColumnParallelLinearWithDelta(BaseLayerWithDelta):
+    def forward(self, x: torch.Tensor):
+        bias = self.base_layer.bias if not self.base_layer.skip_bias_add else None
+        out = self.apply_weights(x, bias)
+        if getattr(self.base_layer, "gather_output", False):
+            out = tensor_model_parallel_all_gather(out)
+        return out, (self.base_layer.bias if self.base_layer.skip_bias_add else None)
+
+    @classmethod
+    def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
+        return type(source_layer) is ColumnParallelLinear or (
+            type(source_layer) is MergedColumnParallelLinear and len(packed_modules_list) == 1)
+
+
+class MergedColumnParallelLinearWithDelta(ColumnParallelLinearWithDelta):
+    """gate_proj + up_proj: one delta tensor set covers both slices (the checkpoint stores the
+    merged, per-rank pre-sharded matrix, as the reference's converter writes it)."""
+
+    def create_delta_weights(self, max_deltas, delta_config, model_config=None):
+        sizes = self.base_layer.output_sizes
+        if not (len(sizes) == 2 and sizes[0] == sizes[1]):
+            raise ValueError("DeltaColumnParallelLinear2Slice requires 2 slices with the same size.")
+        super().create_delta_weights(max_deltas, delta_config, model_config)
+
+    @classmethod
+    def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
+        return type(source_layer) is MergedColumnParallelLinear and len(packed_modules_list) == 2
+
+
+class MergedQKVParallelLinearWithDelta(ColumnParallelLinearWithDelta):
+    def create_delta_weights(self, max_deltas, delta_config, model_config=None):
+        self.q_proj_shard_size = self.base_layer.num_heads * self.base_layer.head_size
+        self.kv_proj_shard_size = self.base_layer.num_kv_heads * self.base_layer.head_size
+        super().create_delta_weights(max_deltas, delta_config, model_config)
+
+    @classmethod
+    def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
+        return type(source_layer) is QKVParallelLinear and len(packed_modules_list) == 3
+
+
+class RowParallelLinearWithDelta(BaseLayerWithDelta):
+    def forward(self, input_):
+        base = self.base_layer
+        if base.input_is_parallel:
+            x = input_
+        else:
+            x = input_[..., base.shard[0]:base.shard[1]].contiguous()
+        out = self.apply_weights(x)
+        if base.reduce_results and base.tp_size > 1:
+            out = tensor_model_parallel_all_reduce(out)
+        return out, None
+
+    @classmethod
+    def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
+        return type(source_layer) is RowParallelLinear
+
+
+_all_delta_classes = (MergedQKVParallelLinearWithDelta, MergedColumnParallelLinearWithDelta,
+                      ColumnParallelLinearWithDelta, RowParallelLinearWithDelta)
+
+
+def from_layer(layer: nn.Module, max_deltas: int, delta_config: DeltaConfig,
+               packed_modules_list: List, model_config=None) -> nn.Module:
+    """Wraps `layer` in the matching delta layer and allocates its slots (returns `layer`
+    unchanged when no delta class applies)."""
+    for cls in _all_delta_classes:
+        if cls.can_replace_layer(layer, delta_config, packed_modules_list, model_config):
+            ret = cls(layer)
+            ret.create_delta_weights(max_deltas, delta_config, model_config)
+            return ret
+    return layer

@@ -1,0 +1,115 @@
+"""Delta layers and slot manager on the GPU, in the shape of the reference's LoRA layer tests
+(serving/tests/lora/test_layers.py): wrap a base layer, fill slots, set a mapping, compare
+with base(x) + x @ delta^T per token."""
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import deltazip_oracle as O
+from tests.gpu_util import dev
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+class TinyModel(nn.Module):
+    supported_delta_modules = ["qkv_proj", "o_proj", "gate_up_proj", "down_proj"]
+    packed_modules_mapping = {"qkv_proj": ["q_proj", "k_proj", "v_proj"],
+                              "gate_up_proj": ["gate_proj", "up_proj"]}
+
+    def __init__(self, hidden=256, inter=384, heads=4):
+        super().__init__()
+        from deltazip_b200 import layers as Ls
+        self.qkv_proj = Ls.QKVParallelLinear(hidden, hidden // heads, heads)
+        self.o_proj = Ls.RowParallelLinear(hidden, hidden)
+        self.gate_up_proj = Ls.MergedColumnParallelLinear(hidden, [inter, inter])
+        self.down_proj = Ls.RowParallelLinear(inter, hidden)
+
+
+def make_delta(model, delta_id, bits, seed):
+    """GPTQ tensors per module from the oracle, then the slot-layout pinned DeltaModel."""
+    from deltazip_b200.models import DeltaModel
+    gptq, dense = {}, {}
+    for name in TinyModel.supported_delta_modules:
+        n, k = getattr(model, name).weight.shape
+        _, ds = O.make_layer(n, k, 1, bits, seed=seed + hash(name) % 97)
+        qw, qz, sc, _ = ds[0]
+        gptq[name] = (torch.from_numpy(qw), torch.from_numpy(qz), torch.from_numpy(sc))
+        dense[name] = O.unpack(qw, qz, sc, bits)
+    return DeltaModel.from_gptq_tensors(delta_id, bits, gptq), dense
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_manager_layers_end_to_end(bits):
+    from deltazip_b200 import layers as Ls
+    from deltazip_b200.config import DeltaConfig
+    from deltazip_b200.models import LRUCacheDeltaModelManager
+    torch.manual_seed(0)
+    model = TinyModel()
+    cfg = DeltaConfig(max_deltas=2, max_bitwidth=bits, max_cpu_deltas=3)
+    mgr = LRUCacheDeltaModelManager(model, 16, 64, 32000, cfg)
+    assert isinstance(model.qkv_proj, Ls.MergedQKVParallelLinearWithDelta)
+    assert isinstance(model.gate_up_proj, Ls.MergedColumnParallelLinearWithDelta)
+    assert isinstance(model.o_proj, Ls.RowParallelLinearWithDelta)
+    assert model.qkv_proj.qweight_stacked.shape == (2, 256 * bits // 128, 2 * 768)
+    assert model.qkv_proj.meta_stacked.shape == (2, 768, 256 // 16)
+
+    dense = {}
+    for did in (11, 12, 13):
+        d, dense[did] = make_delta(model, did, bits, seed=did)
+        mgr.add_delta(d)
+    mgr.activate_delta(11)
+    mgr.activate_delta(12)
+    assert mgr.delta_index_to_id == [11, 12]
+
+    rng = np.random.default_rng(0)
+
+    def check(mapping_ids):
+        mgr.set_delta_mapping(Ls.DeltaMapping(mapping_ids, mapping_ids))
+        for name in TinyModel.supported_delta_modules:
+            layer = getattr(model, name)
+            k = layer.weight.shape[1]
+            x = rng.standard_normal((len(mapping_ids), k), dtype=np.float32).astype(np.float16)
+            y, _ = layer(dev(x))
+            w = layer.weight.detach().cpu().numpy()
+            ref = O.base_linear(x, w).astype(np.float32)
+            for i, did in enumerate(mapping_ids):
+                if did > 0:
+                    ref[i] += x[i].astype(np.float32) @ dense[did][name].astype(np.float32).T
+            assert O.rel_l2(y.cpu().numpy(), ref) <= TOL, name
+
+    check((0, 11, 11, 12, 12, 12, 0))          # unsorted by slot (base tokens at both ends)
+    check((11,) * 5 + (12,) * 4)
+    # LRU: activating a third delta evicts the least recently used one (11) and reuses its slot
+    mgr.activate_delta(13)
+    assert mgr.delta_index_to_id == [13, 12]
+    check((13, 13, 12, 0))
+    with pytest.raises(ValueError):
+        mgr.set_delta_mapping(Ls.DeltaMapping((11,), (11,)))   # 11 is no longer on the GPU
+    # registry capacity 3: adding a 4th evicts the oldest registered delta
+    d4, dense[14] = make_delta(model, 14, bits, seed=14)
+    mgr.add_delta(d4)
+    assert 11 not in mgr.list_deltas() and len(mgr) == 3
+
+
+def test_set_delta_accepts_gptq_tensors_and_reset():
+    from deltazip_b200 import layers as Ls
+    from deltazip_b200.config import DeltaConfig
+    base = Ls.ColumnParallelLinear(128, 256)
+    layer = Ls.from_layer(base, 2, DeltaConfig(max_deltas=2, max_bitwidth=4), ["x"])
+    assert isinstance(layer, Ls.ColumnParallelLinearWithDelta)
+    _, ds = O.make_layer(256, 128, 1, 4, seed=3)
+    qw, qz, sc, _ = ds[0]
+    layer.set_delta(1, 4, torch.from_numpy(qw), torch.from_numpy(qz), torch.from_numpy(sc))
+    idx = torch.tensor([1, 1, -1], device="cuda")
+    layer.set_mapping(idx, indices_len=[3])
+    x = np.random.default_rng(1).standard_normal((3, 128), dtype=np.float32).astype(np.float16)
+    y, _ = layer(dev(x))
+    ref = O.apply_delta(x, base.weight.detach().cpu().numpy(), [None, ds[0]], np.array([1, 1, -1]))
+    assert O.rel_l2(y.cpu().numpy(), ref) <= TOL
+    layer.reset_delta(1)
+    y0, _ = layer(dev(x))
+    assert O.rel_l2(y0.cpu().numpy(), O.base_linear(x, base.weight.detach().cpu().numpy())) <= 2e-3
+    with pytest.raises(ValueError):
+        layer.set_delta(0, 2, torch.from_numpy(qw), torch.from_numpy(qz), torch.from_numpy(sc))
