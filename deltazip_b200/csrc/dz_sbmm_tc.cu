@@ -372,6 +372,14 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_last;
 
+  // Programmatic dependent launch: this grid may be scheduled while its predecessor
+  // in the stream is still draining.  Nothing of the predecessor's output (x, the
+  // segment table, the shared workspace) is touched before this wait, which returns
+  // once the predecessor has completed and its writes are visible; then the next
+  // kernel in the stream is allowed to be scheduled early in turn.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   // ---- early uniform exits (before any barrier or TMEM state exists) ----
   int nwin = 0;
   const int* perm = nullptr;
@@ -1082,8 +1090,17 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
       DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
       di.attr_set[kidx] = true;
     }
-    kern<<<p.grid, kThreads, smem, st>>>(map_w, map_xc, p);
-    DZ_CUDA_OK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DZ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map_w, map_xc, p));
   }
   return DZ_OK;
 }
