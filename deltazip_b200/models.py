@@ -157,6 +157,9 @@ class DeltaModelManager:
         self._active_deltas: Dict[int, None] = {}
         self._last_mapping = None
         self.copy_stream = torch.cuda.Stream(device=device) if self.device.type == "cuda" else None
+        self._loading: Dict[int, int] = {}                 # delta id -> reserved slot (upload in flight)
+        self._slot_ready: List[Optional[torch.cuda.Event]] = [None] * self.delta_slots
+        self._slot_released: List[Optional[torch.cuda.Event]] = [None] * self.delta_slots
         self._create_delta_modules()
         model.delta_manager = self
 
@@ -211,21 +214,15 @@ class DeltaModelManager:
         return self._registered_deltas.get(delta_id)
 
     # -- GPU slots ---------------------------------------------------------------
-    def activate_delta(self, delta_id: int) -> bool:
-        """Uploads the delta into the first free slot (side stream, pinned source); the
-        compute stream is made to wait for the upload before the slot can be used."""
-        if delta_id in self._active_deltas:
-            return False
-        index = next((i for i, d in enumerate(self.delta_index_to_id) if d is None), None)
-        if index is None:
-            raise ValueError("No free delta slots")
-        delta = self._registered_deltas[delta_id]
-        self._active_deltas[delta_id] = None
-        self.delta_index_to_id[index] = delta.id
-        compute = torch.cuda.current_stream(self.device)
-        self.copy_stream.wait_stream(compute)       # earlier kernels may still read the slot
+    def _upload(self, delta: DeltaModel, index: int) -> None:
+        """Enqueues the upload of `delta` into slot `index` on the copy stream.  The copy only
+        waits for the compute work that was enqueued before the slot was last released (an
+        event), so it overlaps with whatever the compute stream is running now."""
         L = lib()
         cs = self.copy_stream.cuda_stream
+        rel = self._slot_released[index]
+        if rel is not None:
+            self.copy_stream.wait_event(rel)
         for name, module in self.modules.items():
             d = delta.get_delta(name)
             if d is None or not d._compressed:
@@ -247,15 +244,61 @@ class DeltaModelManager:
                 else:
                     check(L.dz_slot_upload(dst.data_ptr(), src.data_ptr(), nbytes, 0, cs),
                           "dz_slot_upload")
-        compute.wait_stream(self.copy_stream)
+        ev = torch.cuda.Event()
+        ev.record(self.copy_stream)
+        self._slot_ready[index] = ev
+
+    def prefetch_delta(self, delta_id: int) -> bool:
+        """Starts moving a registered delta into a free GPU slot without making the compute
+        stream wait (the reference prefetches only disk -> pinned host,
+        serving/vllm/delta/worker_manager.py:324-333; here the host -> device leg overlaps with
+        decode as well).  The slot is reserved; activate_delta later publishes it.  Returns
+        False when the delta is already on the GPU or no slot is free."""
+        if delta_id in self._active_deltas or delta_id in self._loading:
+            return False
+        index = next((i for i, d in enumerate(self.delta_index_to_id)
+                      if d is None and i not in self._loading.values()), None)
+        if index is None:
+            return False
+        self._loading[delta_id] = index
+        self._upload(self._registered_deltas[delta_id], index)
+        return True
+
+    def activate_delta(self, delta_id: int) -> bool:
+        """Makes the delta usable by the next forward pass: uploads it if prefetch_delta has not
+        already, and makes the compute stream wait for the upload's event."""
+        if delta_id in self._active_deltas:
+            return False
+        if delta_id not in self._loading:
+            index = next((i for i, d in enumerate(self.delta_index_to_id)
+                          if d is None and i not in self._loading.values()), None)
+            if index is None:
+                raise ValueError("No free delta slots")
+            self._loading[delta_id] = index
+            self._upload(self._registered_deltas[delta_id], index)
+        index = self._loading.pop(delta_id)
+        self._active_deltas[delta_id] = None
+        self.delta_index_to_id[index] = delta_id
+        torch.cuda.current_stream(self.device).wait_event(self._slot_ready[index])
         self._last_mapping = None
         return True
 
     def deactivate_delta(self, delta_id: int) -> bool:
+        if delta_id in self._loading:           # a prefetch that is no longer wanted
+            index = self._loading.pop(delta_id)
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+            self._slot_released[index] = ev
+            return True
         if delta_id not in self._active_deltas:
             return False
         try:
-            self.delta_index_to_id[self.delta_index_to_id.index(delta_id)] = None
+            index = self.delta_index_to_id.index(delta_id)
+            self.delta_index_to_id[index] = None
+            # kernels enqueued so far may still read the slot: a later upload waits for them
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._slot_released[index] = ev
         except ValueError:
             pass
         self._active_deltas.pop(delta_id)
@@ -266,6 +309,7 @@ class DeltaModelManager:
         self._registered_deltas.clear()
         self.delta_index_to_id = [None] * self.delta_slots
         self._active_deltas.clear()
+        self._loading.clear()
         self._last_mapping = None
 
     # -- mapping -------------------------------------------------------------------
@@ -314,7 +358,8 @@ class LRUCacheDeltaModelManager(DeltaModelManager):
         if delta_id in self._active_deltas:
             self._active_deltas.move_to_end(delta_id)
             return False
-        if len(self._active_deltas) >= self.delta_slots:
+        if delta_id not in self._loading and \
+                len(self._active_deltas) + len(self._loading) >= self.delta_slots:
             old, _ = next(iter(self._active_deltas.items()))
             self.deactivate_delta(old)
         ok = super().activate_delta(delta_id)
