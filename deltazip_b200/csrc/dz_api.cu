@@ -28,8 +28,7 @@ static int check_sbmm_args(const dz_sbmm_args* a, bool base_only) {
   if (!a->x || !a->w_base || !a->y) return DZ_ERR_INVALID_ARG;
   int rc = check_shape(a->N, a->K, base_only ? 4 : a->bits);
   if (rc) return rc;
-  if (a->dtype == DZ_DTYPE_BF16) return DZ_ERR_UNSUPPORTED;
-  if (a->dtype != DZ_DTYPE_F16) return DZ_ERR_INVALID_ARG;
+  if (a->dtype != DZ_DTYPE_F16 && a->dtype != DZ_DTYPE_BF16) return DZ_ERR_INVALID_ARG;
   if (!aligned16(a->x) || !aligned16(a->w_base) || !aligned16(a->y)) return DZ_ERR_ALIGNMENT;
   if (!base_only) {
     if (!a->qweight || !a->meta || !a->scales || !a->segments) return DZ_ERR_INVALID_ARG;
@@ -138,6 +137,7 @@ int dz_base_gemm(const dz_sbmm_args* args, void* stream) {
 int dz_sbmm_simt(const dz_sbmm_args* args, void* stream) {
   int rc = check_sbmm_args(args, false);
   if (rc || args->M == 0) return rc;
+  if (args->dtype != DZ_DTYPE_F16) return DZ_ERR_UNSUPPORTED;   // the twin is fp16 only
   return launch_sbmm_simt(*args, false, (cudaStream_t)stream);
 }
 

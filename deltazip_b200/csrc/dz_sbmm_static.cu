@@ -76,8 +76,7 @@ extern "C" int dz_sbmm_static(const dz_sbmm_args* args, void* stream) {
   if (args->N <= 0 || args->K <= 0) return DZ_ERR_INVALID_ARG;
   if (args->N % kTileN != 0 || args->K % kBlockK != 0 || (args->bits != 2 && args->bits != 4))
     return DZ_ERR_SHAPE;
-  if (args->dtype == DZ_DTYPE_BF16) return DZ_ERR_UNSUPPORTED;
-  if (args->dtype != DZ_DTYPE_F16) return DZ_ERR_INVALID_ARG;
+  if (args->dtype != DZ_DTYPE_F16 && args->dtype != DZ_DTYPE_BF16) return DZ_ERR_INVALID_ARG;
   if (args->num_slots <= 0 || args->num_slots > kMaxSlots) return DZ_ERR_INVALID_ARG;
   if (!aligned16(args->x) || !aligned16(args->w_base) || !aligned16(args->y) ||
       !aligned16(args->qweight) || !aligned16(args->meta) || (args->qweight_stride & 15) ||

@@ -41,6 +41,7 @@
 // single, in-order waiter per phase sequence (a parity wait cannot tell phase n
 // from phase n + 2).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -90,7 +91,7 @@ struct Params {
   const uint8_t* scales;
   long long qstride, mstride, sstride;
   const uint8_t* seg;
-  __half* y;
+  void* y;          // fp16 or bf16, like x and W
   float* partials;
   int* counters;
   int* status;
@@ -192,9 +193,16 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 // Instruction descriptor, kind::f16: fp16 A/B (K-major), fp32 accumulate, M = 128.
+// DT: 0 = fp16, 1 = bf16 operands.
+template <int DT>
 __device__ __forceinline__ uint32_t make_idesc(int n, bool sparse) {
-  return (sparse ? (1u << 2) : 0u) | (1u << 4) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(128 >> 4) << 24);
+  return (sparse ? (1u << 2) : 0u) | (1u << 4) | ((uint32_t)DT << 7) | ((uint32_t)DT << 10) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+template <int DT>
+__device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
+  if (DT == 0) reinterpret_cast<__half*>(y)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
 }
 // Shared-memory matrix descriptors (K-major tile, 128-byte swizzle, rows 128 B
 // apart, 8-row groups 1024 B apart) are handled as (lo, hi) 32-bit halves: hi
@@ -305,39 +313,71 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// The fp16 pair (code_lo - zero, code_hi - zero) from the BITS-wide fields at bit P
-// of both half-words of w, without shifting: OR-ing the field into the mantissa
-// of 2^(10-P) gives 2^(10-P) + code (the field has weight 2^-P there), and one
-// subtraction of 2^(10-P) + zero leaves the exact small integer.  P + BITS <= 10.
-template <int BITS, int P>
+// The pair (code_lo - zero, code_hi - zero) as fp16 (DT = 0) or bf16 (DT = 1) from the
+// BITS-wide fields at bit P of both half-words of w, without shifting: OR-ing the field
+// into the mantissa of 2^(m-P) (m = 10 / 7 mantissa bits) gives 2^(m-P) + code (the field
+// has weight 2^-P there), and one subtraction of 2^(m-P) + zero leaves the exact small
+// integer.  Needs P + BITS <= m.
+template <int BITS, int P, int DT>
 __device__ __forceinline__ uint32_t code_pair(uint32_t w) {
+  constexpr uint32_t kMant = DT == 0 ? 10u : 7u;
+  constexpr uint32_t kExpBias = DT == 0 ? 15u : 127u;
+  static_assert(P + BITS <= (DT == 0 ? 10 : 7), "field must sit inside the mantissa");
   constexpr uint32_t kMask = ((((1u << BITS) - 1u) << P)) * 0x00010001u;
-  constexpr uint32_t kMagic = ((25u - P) << 10) * 0x00010001u;
-  constexpr uint32_t kBiasBits = (((25u - P) << 10) | ((1u << (BITS - 1)) << P)) * 0x00010001u;
+  constexpr uint32_t kMagic = ((kExpBias + kMant - P) << kMant) * 0x00010001u;
+  constexpr uint32_t kBiasBits =
+      (((kExpBias + kMant - P) << kMant) | ((1u << (BITS - 1)) << P)) * 0x00010001u;
   uint32_t t;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(w), "n"(kMask), "n"(kMagic));
   uint32_t b = kBiasBits;
-  __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<__half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&hv);
+  if (DT == 0) {
+    __half2 hv = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&hv);
+  } else {
+    __nv_bfloat162 hv =
+        __hsub2(*reinterpret_cast<__nv_bfloat162*>(&t), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&hv);
+  }
 }
-// the 8 (4-bit) or 16 (2-bit) kept values of one packed word -> 4 / 8 fp16 pairs
+// the 8 (4-bit) or 16 (2-bit) kept values of one packed word -> 4 / 8 pairs
+template <int DT>
 __device__ __forceinline__ void expand_word4(uint32_t w, uint32_t* o) {
-  const uint32_t s = w >> 8;
-  o[0] = code_pair<4, 0>(w);
-  o[1] = code_pair<4, 4>(w);
-  o[2] = code_pair<4, 0>(s);
-  o[3] = code_pair<4, 4>(s);
+  if (DT == 0) {
+    const uint32_t s = w >> 8;
+    o[0] = code_pair<4, 0, 0>(w);
+    o[1] = code_pair<4, 4, 0>(w);
+    o[2] = code_pair<4, 0, 0>(s);
+    o[3] = code_pair<4, 4, 0>(s);
+  } else {   // 7 mantissa bits hold one nibble at a time
+    o[0] = code_pair<4, 0, 1>(w);
+    o[1] = code_pair<4, 0, 1>(w >> 4);
+    o[2] = code_pair<4, 0, 1>(w >> 8);
+    o[3] = code_pair<4, 0, 1>(w >> 12);
+  }
 }
+template <int DT>
 __device__ __forceinline__ void expand_word2(uint32_t w, uint32_t* o) {
-  const uint32_t s = w >> 10;
-  o[0] = code_pair<2, 0>(w);
-  o[1] = code_pair<2, 2>(w);
-  o[2] = code_pair<2, 4>(w);
-  o[3] = code_pair<2, 6>(w);
-  o[4] = code_pair<2, 8>(w);
-  o[5] = code_pair<2, 0>(s);
-  o[6] = code_pair<2, 2>(s);
-  o[7] = code_pair<2, 4>(s);
+  if (DT == 0) {
+    const uint32_t s = w >> 10;
+    o[0] = code_pair<2, 0, 0>(w);
+    o[1] = code_pair<2, 2, 0>(w);
+    o[2] = code_pair<2, 4, 0>(w);
+    o[3] = code_pair<2, 6, 0>(w);
+    o[4] = code_pair<2, 8, 0>(w);
+    o[5] = code_pair<2, 0, 0>(s);
+    o[6] = code_pair<2, 2, 0>(s);
+    o[7] = code_pair<2, 4, 0>(s);
+  } else {
+    const uint32_t s = w >> 6, u = w >> 12;
+    o[0] = code_pair<2, 0, 1>(w);
+    o[1] = code_pair<2, 2, 1>(w);
+    o[2] = code_pair<2, 4, 1>(w);
+    o[3] = code_pair<2, 0, 1>(s);
+    o[4] = code_pair<2, 2, 1>(s);
+    o[5] = code_pair<2, 4, 1>(s);
+    o[6] = code_pair<2, 0, 1>(u);
+    o[7] = code_pair<2, 2, 1>(u);
+  }
 }
 
 // CTA that owns unit u when `total` units are split evenly over `grid` CTAs
@@ -361,7 +401,7 @@ struct Ring {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int BITS, bool INSTR>
+template <int BITS, int DT, bool INSTR>
 __global__ void __launch_bounds__(kThreads, 1)
 sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xc,
                const Params p) {
@@ -578,7 +618,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       int pacc = 1;
       long long t_acc = 0, t_full = 0;
       const long long t_start = clock64();
-      const uint32_t idesc_base = make_idesc(p.cols, false);
+      const uint32_t idesc_base = make_idesc<DT>(p.cols, false);
       for (int u = u_begin; u < u_end;) {
         const int ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
@@ -634,7 +674,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                t_ready);
             tc_fence_after();
             const uint32_t win_lo = desc_lo(s_winbuf + buf * kWinBytes);
-            const uint32_t idesc = make_idesc(ws.ncols, true);
+            const uint32_t idesc = make_idesc<DT>(ws.ncols, true);
             const uint32_t dcol = tmem_base + p.dcols + ws.col0;
             const uint32_t acol = tmem_base + a_col0 + buf * 32;
             const uint32_t ecol = tmem_base + e_col0 + buf * 4;
@@ -724,12 +764,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const uint4 cw = *reinterpret_cast<const uint4*>(raw + h * 2048 + r * 16);
               const uint32_t wv[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
-              for (int wi = 0; wi < 4; ++wi) expand_word4(wv[wi], o + wi * 4);
+              for (int wi = 0; wi < 4; ++wi) expand_word4<DT>(wv[wi], o + wi * 4);
             } else {
               const uint2 cw = *reinterpret_cast<const uint2*>(raw + h * 1024 + r * 8);
               const uint32_t wv[2] = {cw.x, cw.y};
 #pragma unroll
-              for (int wi = 0; wi < 2; ++wi) expand_word2(wv[wi], o + wi * 8);
+              for (int wi = 0; wi < 2; ++wi) expand_word2<DT>(wv[wi], o + wi * 8);
             }
             // compressed A of this half: 32 fp16 = 16 columns of the row's lane
             tmem_st16(lane_addr + a_col0 + buf * 32 + h * 16, o);
@@ -811,7 +851,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int prow = p.row0 + c * 16 + i;
             if (prow < p.M) {
               const int tok = perm ? perm[prow] : prow;
-              p.y[(size_t)tok * p.N + n0 + r] = __float2half_rn(__uint_as_float(v[i]));
+              store_out<DT>(p.y, (size_t)tok * p.N + n0 + r, __uint_as_float(v[i]));
             }
           }
         } else {
@@ -875,7 +915,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const int prow = p.row0 + cb + i;
               if (prow < p.M) {
                 const int tok = perm ? perm[prow] : prow;
-                p.y[(size_t)tok * p.N + n0 + r] = __float2half_rn(sum[i]);
+                store_out<DT>(p.y, (size_t)tok * p.N + n0 + r, sum[i]);
               }
             }
           }
@@ -955,14 +995,14 @@ EncodeTiledFn encode_fn() {
 }
 
 // fp16 row-major [rows, K] matrix, box = 64 (k) x box_rows, 128-byte swizzle
-int encode_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+int encode_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows, int dt) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return DZ_ERR_CUDA;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+  CUresult r = fn(map, dt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? DZ_OK : DZ_ERR_CUDA;
@@ -972,25 +1012,26 @@ int encode_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows)
 // keeps the driver's encode call off the per-layer launch path.
 struct MapKey {
   const void* ptr;
-  int rows, K, box;
+  int rows, K, box, dt;
 };
 struct MapEntry {
   MapKey key;
   CUtensorMap map;
 };
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows, int dt) {
   constexpr int kEntries = 1024;
   static thread_local MapEntry* cache = nullptr;
   if (!cache) cache = new MapEntry[kEntries]();
   const uintptr_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull;
   MapEntry& e = cache[((h >> 40) ^ (uintptr_t)box_rows) % kEntries];
-  if (e.key.ptr == ptr && e.key.rows == rows && e.key.K == K && e.key.box == box_rows) {
+  if (e.key.ptr == ptr && e.key.rows == rows && e.key.K == K && e.key.box == box_rows &&
+      e.key.dt == dt) {
     *map = e.map;
     return DZ_OK;
   }
-  int rc = encode_map(map, ptr, rows, K, box_rows);
+  int rc = encode_map(map, ptr, rows, K, box_rows, dt);
   if (rc == DZ_OK) {
-    e.key = MapKey{ptr, rows, K, box_rows};
+    e.key = MapKey{ptr, rows, K, box_rows, dt};
     e.map = *map;
   }
   return rc;
@@ -998,7 +1039,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
 
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[4] = {false, false, false, false};
+  bool attr_set[6] = {false, false, false, false, false, false};
 };
 DeviceInfo& device_info(int dev) {
   static DeviceInfo info[64];
@@ -1043,7 +1084,8 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   }
 
   CUtensorMap map_w, map_xc;
-  int rc = make_map(&map_w, a.w_base, a.N, a.K, 128);
+  const int dt = (a.dtype == DZ_DTYPE_BF16) ? 1 : 0;
+  int rc = make_map(&map_w, a.w_base, a.N, a.K, 128, dt);
   if (rc) return rc;
 
   Params p;
@@ -1061,13 +1103,15 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.scales = (const uint8_t*)a.scales;
   p.qstride = a.qweight_stride; p.mstride = a.meta_stride; p.sstride = a.scales_stride;
   p.seg = base_only ? nullptr : (const uint8_t*)a.segments;
-  p.y = (__half*)a.y;
+  p.y = a.y;
   p.status = reinterpret_cast<int*>(ws + kWsStatus);
   p.counters = reinterpret_cast<int*>(ws + kWsCounters);
   p.partials = reinterpret_cast<float*>(ws + kWsPartials);
 
   const bool instr = (p.debug & 16) != 0;
-  const int kidx = ((a.bits == 2) ? 0 : 1) + (instr ? 2 : 0);
+  const int dtq = (a.dtype == DZ_DTYPE_BF16) ? 1 : 0;
+  if (instr && dtq) return DZ_ERR_UNSUPPORTED;
+  const int kidx = ((a.bits == 2) ? 0 : 1) + (instr ? 2 : (dtq ? 4 : 0));
   const int num_tb = (a.M + kTokenBlock - 1) / kTokenBlock;
   for (int tb = 0; tb < num_tb; ++tb) {
     p.token_block = tb;
@@ -1081,11 +1125,12 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + 2 * p.nclass * kWinBytes;
     p.r_per_class = min(4, (kSmemBudget - fixed) / (p.nclass * kRStage));
     if (p.r_per_class < 2 || p.nclass * p.r_per_class > kMaxR) return DZ_ERR_UNSUPPORTED;
-    rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols);
+    rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols, dt);
     if (rc) return rc;
     const size_t smem = (size_t)fixed + (size_t)p.nclass * p.r_per_class * kRStage + 1024;
-    auto kern = instr ? ((a.bits == 2) ? sbmm_tc_kernel<2, true> : sbmm_tc_kernel<4, true>)
-                      : ((a.bits == 2) ? sbmm_tc_kernel<2, false> : sbmm_tc_kernel<4, false>);
+    auto kern = instr ? ((a.bits == 2) ? sbmm_tc_kernel<2, 0, true> : sbmm_tc_kernel<4, 0, true>)
+                : dt  ? ((a.bits == 2) ? sbmm_tc_kernel<2, 1, false> : sbmm_tc_kernel<4, 1, false>)
+                      : ((a.bits == 2) ? sbmm_tc_kernel<2, 0, false> : sbmm_tc_kernel<4, 0, false>);
     if (!di.attr_set[kidx]) {
       DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
       di.attr_set[kidx] = true;

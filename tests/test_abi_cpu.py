@@ -58,9 +58,8 @@ def test_argument_validation_without_gpu(handle):
     assert L.dz_sbmm(ctypes.byref(a), None) == _lib.DZ_ERR_SHAPE
     a = _lib.SbmmArgs(x=8, w_base=16, y=16, M=4, N=128, K=64, bits=4, num_slots=1)
     assert L.dz_sbmm(ctypes.byref(a), None) == _lib.DZ_ERR_ALIGNMENT
-    a = _lib.SbmmArgs(x=16, w_base=16, y=16, M=4, N=128, K=64, bits=4, num_slots=1,
-                      dtype=_lib.DZ_DTYPE_BF16)
-    assert L.dz_sbmm(ctypes.byref(a), None) == _lib.DZ_ERR_UNSUPPORTED
+    a = _lib.SbmmArgs(x=16, w_base=16, y=16, M=4, N=128, K=64, bits=4, num_slots=1, dtype=7)
+    assert L.dz_sbmm(ctypes.byref(a), None) == _lib.DZ_ERR_INVALID_ARG      # unknown dtype
     assert L.dz_build_segments(None, 0, 4, 2, None, None) == _lib.DZ_ERR_INVALID_ARG
     assert L.dz_convert_from_gptq(None, None, None, 128, 64, 4, None, None, None, None, None) \
         == _lib.DZ_ERR_INVALID_ARG

@@ -179,3 +179,35 @@ def test_prefetch_overlaps_decode_and_stays_correct():
             if did > 0:
                 ref[i] += x[i].astype(np.float32) @ dense[did][name].astype(np.float32).T
         assert O.rel_l2(y.cpu().numpy(), ref) <= TOL, name
+
+
+def test_delta_checkpoint_roundtrip(tmp_path):
+    """A delta saved with the reference's artefact layout (deltazip-compressed.safetensors with
+    keys "{module}.{tp_rank}.{qweight|scales|meta}" plus compress_config.json,
+    serving/vllm/delta/models.py:239-258) loads into pinned host memory and serves."""
+    from safetensors.torch import save_file
+    from deltazip_b200 import layers as Ls
+    from deltazip_b200.config import CompressionConfig, DeltaConfig
+    from deltazip_b200.models import DeltaModel, DeltaModelManager
+    torch.manual_seed(1)
+    model = TinyModel()
+    mgr = DeltaModelManager(model, 8, 32, 32000, DeltaConfig(max_deltas=1, max_bitwidth=4))
+    d, dense = make_delta(model, 5, 4, seed=5)
+    tensors = {}
+    for name, w in d.deltas.items():
+        tensors[f"{name}.0.qweight"] = w.qweight.clone()
+        tensors[f"{name}.0.scales"] = w.scales.clone()
+        tensors[f"{name}.0.meta"] = w.meta.clone()
+    save_file(tensors, str(tmp_path / "deltazip-compressed.safetensors"))
+    CompressionConfig(bits=4, prunen=2, prunem=4).save_pretrained(str(tmp_path))
+    loaded = DeltaModel.from_checkpoint(str(tmp_path), 5, tp_rank=0)
+    assert loaded.bitwidth == 4 and set(loaded.deltas) == set(d.deltas)
+    assert all(w.qweight.is_pinned() for w in loaded.deltas.values())
+    mgr.add_delta(loaded)
+    mgr.activate_delta(5)
+    mgr.set_delta_mapping(Ls.DeltaMapping((5, 5, 0), (5,)))
+    x = np.random.default_rng(2).standard_normal((3, 256), dtype=np.float32).astype(np.float16)
+    y, _ = model.o_proj(dev(x))
+    ref = O.base_linear(x, model.o_proj.weight.detach().cpu().numpy()).astype(np.float32)
+    ref[:2] += x[:2].astype(np.float32) @ dense["o_proj"].astype(np.float32).T
+    assert O.rel_l2(y.cpu().numpy(), ref) <= TOL

@@ -148,3 +148,29 @@ def test_deterministic_across_runs():
     for _ in range(5):
         y = ops.sbmm(xd, layer.qweight, layer.scales, layer.meta, seg, layer.w)
         assert torch.equal(y, y0)
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_bf16_activations_and_base(bits):
+    """bf16 base weights / activations (scales stay fp16, as in the reference's layers,
+    serving/vllm/delta/layers_marlin.py:319-325).  Reference: the same formula in float32 on
+    the bf16 values; tolerance rel-L2 <= 1e-2 (bf16 keeps 8 significant bits)."""
+    from deltazip_b200 import ops
+    layer = DeviceLayer(512, 1024, 6, bits, seed=31)
+    x_np, idx_np = O.make_tokens(75, 1024, 6, seed=31, base_frac=0.15)
+    xb = dev(x_np).to(torch.bfloat16)
+    wb = layer.w.to(torch.bfloat16)
+    seg = ops.Segments(75, 6, "cuda").build(dev(idx_np))
+    y = ops.sbmm(xb, layer.qweight, layer.scales, layer.meta, seg, wb)
+    assert y.dtype == torch.bfloat16
+    ref = xb.float() @ wb.float().t()
+    dense = [torch.from_numpy(d).cuda().float() for d in layer.dense()]
+    idx = torch.from_numpy(idx_np).cuda()
+    for d in range(6):
+        rows = idx == d
+        ref[rows] += xb[rows].float() @ dense[d].t()
+    err = O.rel_l2(y.float().cpu().numpy(), ref.cpu().numpy())
+    assert err <= TOL, err
+    assert ops.read_status() == 0
+    yb = ops.base_gemm(xb, wb)
+    assert O.rel_l2(yb.float().cpu().numpy(), (xb.float() @ wb.float().t()).cpu().numpy()) <= 5e-3
