@@ -73,6 +73,8 @@ _SIGNATURES = {
     "dz_base_gemm": (c_int, [POINTER(SbmmArgs), c_void_p]),
     "dz_sbmm_static": (c_int, [POINTER(SbmmArgs), c_void_p]),
     "dz_sbmm_static_max_tokens": (c_int, []),
+    "dz_delta_embedding": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "dz_slot_upload": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "dz_slot_reset": (c_int, [c_void_p, c_size_t, c_void_p]),
     "dz_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),

@@ -255,3 +255,52 @@ def apply_delta(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: 
         _segment_cache[key] = seg
     seg.build(indices)
     return sbmm(x, qweight_stacked, scales_stacked, meta_stacked, seg, base_weight)
+
+
+# ---------------------------------------------------------------------------
+# per-delta embedding / lm_head (full replacement tables, not additive deltas)
+# ---------------------------------------------------------------------------
+
+def _index_code(indices: torch.Tensor) -> int:
+    if indices.dtype == torch.int64:
+        return _lib.DZ_INDEX_I64
+    if indices.dtype == torch.int32:
+        return _lib.DZ_INDEX_I32
+    raise ValueError("indices must be int32 or int64")
+
+
+def apply_delta_embed(x: torch.Tensor, delta_weights: torch.Tensor, indices: torch.Tensor,
+                      base_weight: torch.Tensor) -> torch.Tensor:
+    """Embedding lookup with a replacement table per delta (reference:
+    serving/vllm/delta/deltazip_marlin.py:56-86).  x: token ids [M]; delta_weights:
+    [D, vocab, hidden]; indices: slot per token (-1 = base_weight [vocab, hidden])."""
+    _need_cuda(x, delta_weights, indices, base_weight)
+    tokens = x.reshape(-1).to(torch.int64).contiguous()
+    indices = indices.reshape(-1).contiguous()
+    m = tokens.numel()
+    vocab, hidden = base_weight.shape
+    out = torch.empty((m, hidden), dtype=base_weight.dtype, device=base_weight.device)
+    d = delta_weights.shape[0] if delta_weights is not None and delta_weights.numel() else 0
+    check(lib().dz_delta_embedding(
+        tokens.data_ptr(), indices.data_ptr(), _index_code(indices), m, hidden,
+        base_weight.data_ptr(), delta_weights.data_ptr() if d else None,
+        delta_weights.stride(0) * delta_weights.element_size() if d else 0, d, vocab,
+        out.data_ptr(), None, _stream()), "dz_delta_embedding")
+    return out.reshape(*x.shape, hidden)
+
+
+def apply_delta_uncompressed(x: torch.Tensor, delta_weights: torch.Tensor, indices: torch.Tensor,
+                             base_embedding: torch.Tensor) -> torch.Tensor:
+    """lm_head with a full replacement matrix per delta: rows with slot d are multiplied by
+    delta_weights[d], rows with -1 by base_embedding (reference:
+    serving/vllm/delta/deltazip_marlin.py:21-53; like it, this loops over the distinct ids,
+    which costs one host synchronisation).  Each group runs on the dense tcgen05 GEMM."""
+    _need_cuda(x, delta_weights, indices, base_embedding)
+    x2 = x.reshape(-1, x.shape[-1])
+    n = base_embedding.shape[0]
+    out = torch.zeros((x2.shape[0], n), dtype=x.dtype, device=x.device)
+    for d in torch.unique(indices).tolist():
+        rows = (indices == d).nonzero(as_tuple=True)[0]
+        w = base_embedding if d < 0 else delta_weights[d]
+        out[rows] = base_gemm(x2[rows].contiguous(), w.contiguous())
+    return out.reshape(*x.shape[:-1], n)

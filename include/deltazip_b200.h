@@ -158,6 +158,18 @@ int dz_sbmm_static_max_tokens(void);
 int dz_base_gemm(const dz_sbmm_args* args, void* stream);
 
 /*
+ * Per-delta embedding: y[i] = table_{indices[i]}[token_ids[i]] (2-byte elements, `hidden`
+ * per row), indices[i] == -1 selects `base_table`; the delta tables are full replacement
+ * tables stacked `table_stride_bytes` apart.  Replaces apply_delta_embed
+ * (serving/vllm/delta/deltazip_marlin.py:56-86).  Token ids outside [0, vocab) give a
+ * zero row and DZ_ERR_INVALID_ARG in `status_word` (device int, may be NULL).
+ */
+int dz_delta_embedding(const int64_t* token_ids, const void* indices, int index_dtype, int M,
+                       int hidden, const void* base_table, const void* delta_tables,
+                       int64_t table_stride_bytes, int num_slots, int64_t vocab, void* y,
+                       int* status_word, void* stream);
+
+/*
  * Delta swap-in: one asynchronous host->device copy of a delta's slot bytes
  * from PINNED host memory on `copy_stream`, preceded by a zero fill of the
  * destination when `zero_first` != 0 (the reference resets a slot before it

@@ -211,3 +211,25 @@ def test_delta_checkpoint_roundtrip(tmp_path):
     ref = O.base_linear(x, model.o_proj.weight.detach().cpu().numpy()).astype(np.float32)
     ref[:2] += x[:2].astype(np.float32) @ dense["o_proj"].astype(np.float32).T
     assert O.rel_l2(y.cpu().numpy(), ref) <= TOL
+
+
+def test_per_delta_embedding_and_lm_head():
+    """Replacement tables per delta for embedding and lm_head, against the reference's
+    semantics (rows of slot d use table d, -1 uses the base table)."""
+    from deltazip_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(0)
+    vocab, hidden, d = 1024, 256, 3
+    base = torch.randn((vocab, hidden), generator=g, device="cuda").half()
+    tabs = torch.randn((d, vocab, hidden), generator=g, device="cuda").half()
+    tok = torch.randint(0, vocab, (37,), generator=g, device="cuda")
+    idx = torch.randint(-1, d, (37,), generator=g, device="cuda")
+    y = ops.apply_delta_embed(tok, tabs, idx, base)
+    ref = torch.where((idx < 0)[:, None], base[tok], tabs[idx.clamp(min=0), tok])
+    assert torch.equal(y, ref)
+    x = torch.randn((37, hidden), generator=g, device="cuda").half()
+    logits = ops.apply_delta_uncompressed(x, tabs, idx, base)
+    ref = torch.empty((37, vocab), device="cuda")
+    for i in range(37):
+        w = base if idx[i] < 0 else tabs[idx[i]]
+        ref[i] = x[i].float() @ w.float().t()
+    assert O.rel_l2(logits.float().cpu().numpy(), ref.cpu().numpy()) <= 2e-3
