@@ -71,6 +71,7 @@ constexpr int kTmemCols = 512;
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
 constexpr int kMaxCtas = 160;
 constexpr int kSmemBudget = 216 * 1024;
+constexpr int kPrefetchTiles = 8;               // W half-tiles prefetched to L2 in the prologue
 
 // TMEM columns: D_base [0, dcols), D_delta [dcols, 2 dcols), then 32 columns of
 // expanded A per buffer, then 4 columns of metadata per buffer.
@@ -154,18 +155,6 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int* status) {
   if (mbar_try_wait(bar, parity)) return;
   mbar_wait_slow(bar, parity, abort_flag, status);
-}
-// wait + cycle accounting (experiments only)
-template <bool INSTR>
-__device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int* status, long long& acc) {
-  if (INSTR) {
-    const long long t0 = clock64();
-    mbar_wait(bar, parity, abort_flag, status);
-    acc += clock64() - t0;
-  } else {
-    mbar_wait(bar, parity, abort_flag, status);
-  }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
                                             uint32_t bar) {
@@ -278,6 +267,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
         "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
         "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7])
       : "r"(taddr)
       : "memory");
 }
@@ -412,35 +409,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_last;
 
-  // Programmatic dependent launch: this grid may be scheduled while its predecessor
-  // in the stream is still draining.  Nothing of the predecessor's output (x, the
-  // segment table, the shared workspace) is touched before this wait, which returns
-  // once the predecessor has completed and its writes are visible; then the next
-  // kernel in the stream is allowed to be scheduled early in turn.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-  // ---- early uniform exits (before any barrier or TMEM state exists) ----
-  int nwin = 0;
-  const int* perm = nullptr;
-  const int* slot_of = nullptr;
-  const Window* gwin = nullptr;
-  if (p.seg) {
-    const SegHeader* hdr = reinterpret_cast<const SegHeader*>(p.seg);
-    if (p.tokens_sorted && !hdr->sorted) {
-      if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(p.status, 0, (int)DZ_ERR_INVALID_ARG);
-      return;
-    }
-    const SegLayout lay = seg_layout(hdr->capacity_M, hdr->num_slots);
-    perm = reinterpret_cast<const int*>(p.seg + lay.perm);
-    slot_of = reinterpret_cast<const int*>(p.seg + lay.slot_of);
-    if (!p.base_only) {
-      const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
-      const int win_begin = bb[p.token_block];
-      nwin = min(bb[p.token_block + 1] - win_begin, kMaxWin);
-      gwin = reinterpret_cast<const Window*>(p.seg + lay.windows) + win_begin;
-    }
-  }
+  // INSTR only: per-CTA wall-clock marks of the last launch (8 x u64 per CTA) in the upper
+  // part of the counter region
+  unsigned long long* const tl =
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.counters) + 4096) +
+      (size_t)blockIdx.x * 8;
+  if (INSTR && threadIdx.x == 0) tl[0] = globaltimer();
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -473,17 +447,23 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint64_t* bar_acc_full = bar_a_free + kMaxBuf;
   uint64_t* bar_acc_empty = bar_acc_full + 1;
 
+  // ---- this CTA's unit range ----
+  const int cta = blockIdx.x;
+  const long long U = p.total_units;
+  const int u_begin = (int)((long long)cta * U / p.grid);
+  const int u_end = (int)((long long)(cta + 1) * U / p.grid);
+  const int KU = p.num_kunits;
+
+  // ---- part of the prologue that reads nothing an earlier kernel may still be writing ----
+  // (barriers whose arrival counts do not depend on the batch, tensor memory, L2 prefetches of
+  // the first W tiles).  Under programmatic dependent launch this runs while the predecessor's
+  // last CTAs are still draining.
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxW; ++i) {
       mbar_init(smem_u32(&bar_w_full[i]), 1);
       mbar_init(smem_u32(&bar_w_empty[i]), 1);
     }
-    for (int i = 0; i < kMaxX; ++i) {
-      mbar_init(smem_u32(&bar_x_full[i]), 1);
-      // freed by the base issuer's commit and, when there are windows, by every
-      // thread of every active expansion warpgroup
-      mbar_init(smem_u32(&bar_x_empty[i]), 1 + (nwin > 0 ? 128 * C : 0));
-    }
+    for (int i = 0; i < kMaxX; ++i) mbar_init(smem_u32(&bar_x_full[i]), 1);
     for (int i = 0; i < kMaxR; ++i) {
       mbar_init(smem_u32(&bar_r_full[i]), 1);
       mbar_init(smem_u32(&bar_r_empty[i]), 128);
@@ -492,13 +472,23 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(smem_u32(&bar_a_ready[i]), 128);
       mbar_init(smem_u32(&bar_a_free[i]), 1);
     }
-    mbar_init(smem_u32(bar_acc_full), 1 + (nwin > 0 ? C : 0));
     mbar_init(smem_u32(bar_acc_empty), 128 * kNumWG);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xc) : "memory");
+    // pull the first W tiles of this CTA's range towards L2 (a prefetch consumes no data, so it
+    // is safe whatever the predecessor writes)
+    int issued = 0;
+    for (int u = u_begin; u < u_end && issued < kPrefetchTiles && !(p.debug & 1); ++u) {
+      const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
+      const int nhalf = min(2, (p.K - k0) / kBlockK);
+      for (int h = 0; h < nhalf; ++h, ++issued)
+        asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&map_w),
+                     "r"(k0 + h * kBlockK), "r"(n0)
+                     : "memory");
+    }
   }
   if (warp == kWarpBase) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -506,6 +496,49 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                  "n"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  // Programmatic dependent launch: this grid may be scheduled while its predecessor in the
+  // stream is still draining.  Nothing the predecessor writes (x, the segment table, the
+  // shared workspace) is touched before this wait, which returns once the predecessor has
+  // completed and its writes are visible; then the next kernel in the stream is allowed to be
+  // scheduled early in turn.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (INSTR && threadIdx.x == 0) tl[1] = globaltimer();
+
+  // ---- the batch: windows and per-column slots of this token block ----
+  int nwin = 0;
+  bool bad = false;
+  const int* perm = nullptr;
+  const int* slot_of = nullptr;
+  const Window* gwin = nullptr;
+  if (p.seg) {
+    const SegHeader* hdr = reinterpret_cast<const SegHeader*>(p.seg);
+    bad = p.tokens_sorted && !hdr->sorted;
+    const SegLayout lay = seg_layout(hdr->capacity_M, hdr->num_slots);
+    perm = reinterpret_cast<const int*>(p.seg + lay.perm);
+    slot_of = reinterpret_cast<const int*>(p.seg + lay.slot_of);
+    if (!p.base_only && !bad) {
+      const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
+      const int win_begin = bb[p.token_block];
+      nwin = min(bb[p.token_block + 1] - win_begin, kMaxWin);
+      gwin = reinterpret_cast<const Window*>(p.seg + lay.windows) + win_begin;
+    }
+  }
+  if (threadIdx.x == 0) {
+    // freed by the base issuer's commit and, when there are windows, by every thread of every
+    // active expansion warpgroup
+    for (int i = 0; i < kMaxX; ++i)
+      mbar_init(smem_u32(&bar_x_empty[i]), 1 + (nwin > 0 ? 128 * C : 0));
+    mbar_init(smem_u32(bar_acc_full), 1 + (nwin > 0 ? C : 0));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (bad && blockIdx.x == 0) atomicCAS(p.status, 0, (int)DZ_ERR_INVALID_ARG);
   }
   for (int i = threadIdx.x; i < kTokenBlock; i += kThreads) {
     const int prow = p.row0 + i;
@@ -520,11 +553,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     ws.lohi = (w.lo - w.col0) | ((w.hi - w.col0) << 16);
     s_win[i] = ws;
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = s_tmem_base;
-  volatile int* abort_flag = &s_abort;
   // D_delta starts at zero (the delta MMAs always accumulate)
   if (warp >= kFirstWGWarp && nwin > 0) {
     const int wg = (warp - kFirstWGWarp) >> 2;
@@ -536,16 +564,13 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
 
-  // ---- this CTA's unit range ----
-  const int cta = blockIdx.x;
-  const long long U = p.total_units;
-  const int u_begin = (int)((long long)cta * U / p.grid);
-  const int u_end = (int)((long long)(cta + 1) * U / p.grid);
-  const int KU = p.num_kunits;
+  if (INSTR && threadIdx.x == 0) tl[2] = globaltimer();
   const uint32_t a_col0 = 2 * p.dcols;          // TMEM column of expanded-A buffer 0
   const uint32_t e_col0 = a_col0 + nbuf * 32;   // TMEM column of metadata buffer 0
 
-  if (warp == kWarpWX) {
+  if (bad) {
+    // rejected batch: nothing runs
+  } else if (warp == kWarpWX) {
     // ====================== TMA producer: W tiles and x half-tiles ======================
     if (lane == 0) {
       Ring rw(p.w_stages, 1), rx(p.x_stages, 1);
@@ -616,22 +641,21 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (lane == 0) {
       Ring rw(p.w_stages, 0), rx(p.x_stages, 0);
       int pacc = 1;
-      long long t_acc = 0, t_full = 0;
-      const long long t_start = clock64();
       const uint32_t idesc_base = make_idesc<DT>(p.cols, false);
       for (int u = u_begin; u < u_end;) {
         const int ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
-        mbar_wait_t<INSTR>(smem_u32(bar_acc_empty), pacc, abort_flag, p.status, t_acc);
+        mbar_wait(smem_u32(bar_acc_empty), pacc, abort_flag, p.status);
         pacc ^= 1;
         tc_fence_after();
         uint32_t acc = 0;
         for (int ku = ku0; ku < ku1; ++ku) {
           const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
-            mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_full);
-            mbar_wait_t<INSTR>(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status, t_full);
+            mbar_wait(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status);
+            mbar_wait(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status);
             tc_fence_after();
+            if (INSTR && u == u_begin && ku == ku0 && h == 0) tl[3] = globaltimer();
             umma_ss_x4(tmem_base, desc_lo(s_wring + rw.idx * kWTile),
                        desc_lo(s_xring + rx.idx * p.xb_bytes), idesc_base, acc);
             acc = 1;
@@ -644,12 +668,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         umma_commit(smem_u32(bar_acc_full));
         u += ku1 - ku0;
       }
-      if (INSTR) {
-        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
-        atomicAdd(st + 0, (unsigned long long)(clock64() - t_start));
-        atomicAdd(st + 1, (unsigned long long)t_acc);
-        atomicAdd(st + 2, (unsigned long long)t_full);
-      }
+      if (INSTR) tl[4] = globaltimer();
     }
   } else if (warp >= kWarpIssuer0 && warp < kWarpIssuer0 + 4) {
     // =========================== delta MMA issuer of class t ===========================
@@ -657,12 +676,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (lane == 0 && t < C && nwin > 0) {
       const int cnt_t = (nwin - t + C - 1) / C;
       int pacc = 1, n = 0;
-      long long t_acc = 0, t_ready = 0;
-      const long long t_start = clock64();
       for (int u = u_begin; u < u_end;) {
         const int ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
-        mbar_wait_t<INSTR>(smem_u32(bar_acc_empty), pacc, abort_flag, p.status, t_acc);
+        mbar_wait(smem_u32(bar_acc_empty), pacc, abort_flag, p.status);
         pacc ^= 1;
         tc_fence_after();
         for (int ku = ku0; ku < ku1; ++ku) {
@@ -670,8 +687,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           for (int j = 0; j < cnt_t; ++j, ++n) {
             const WinS ws = s_win[t + j * C];
             const int buf = t + C * (n & 1);
-            mbar_wait_t<INSTR>(smem_u32(&bar_a_ready[buf]), (n >> 1) & 1, abort_flag, p.status,
-                               t_ready);
+            mbar_wait(smem_u32(&bar_a_ready[buf]), (n >> 1) & 1, abort_flag, p.status);
             tc_fence_after();
             const uint32_t win_lo = desc_lo(s_winbuf + buf * kWinBytes);
             const uint32_t idesc = make_idesc<DT>(ws.ncols, true);
@@ -685,12 +701,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         umma_commit(smem_u32(bar_acc_full));
         u += ku1 - ku0;
-      }
-      if (INSTR && t == 0) {
-        unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
-        atomicAdd(st + 3, (unsigned long long)(clock64() - t_start));
-        atomicAdd(st + 4, (unsigned long long)t_acc);
-        atomicAdd(st + 5, (unsigned long long)t_ready);
       }
     }
   } else if (warp >= kFirstWGWarp) {
@@ -707,9 +717,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int pacc = 0, n = 0, rs = 0;
     uint32_t rpar = 0;
     bool cta_first_fragment = true;
-    long long t_deq = 0, t_copy = 0, t_sync = 0, t_epi = 0;
-    long long t_rfull = 0, t_afree = 0, t_xfull = 0, t_accf = 0;
-    const long long t_start = clock64();
 
     for (int u = u_begin; u < u_end;) {
       const int tile = u / KU, ku0 = u % KU;
@@ -740,7 +747,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint8_t* xsrc1 = nullptr;
         int xslot0 = 0, xslot1 = 0;
         for (int h = 0; h < nhalf; ++h) {
-          mbar_wait_t<INSTR>(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status, t_xfull);
+          mbar_wait(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status);
           if (h == 0) { xsrc0 = g_xring + rx.idx * p.xb_bytes; xslot0 = rx.idx; }
           else { xsrc1 = g_xring + rx.idx * p.xb_bytes; xslot1 = rx.idx; }
           rx.advance();
@@ -749,12 +756,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const WinS ws = s_win[wg + j * C];
           const int buf = wg + C * (n & 1);
           const int rslot = wg * p.r_per_class + rs;
-          mbar_wait_t<INSTR>(smem_u32(&bar_r_full[rslot]), rpar, abort_flag, p.status, t_rfull);
+          mbar_wait(smem_u32(&bar_r_full[rslot]), rpar, abort_flag, p.status);
           if (++rs == p.r_per_class) { rs = 0; rpar ^= 1; }
-          mbar_wait_t<INSTR>(smem_u32(&bar_a_free[buf]), ((n >> 1) & 1) ^ 1, abort_flag, p.status,
-                             t_afree);
+          mbar_wait(smem_u32(&bar_a_free[buf]), ((n >> 1) & 1) ^ 1, abort_flag, p.status);
           tc_fence_after();
-          long long tc0 = INSTR ? clock64() : 0;
           const uint8_t* raw = g_rring + rslot * kRStage;
           uint8_t* const my_win = g_winbuf + buf * kWinBytes;
           uint32_t mw[4] = {0, 0, 0, 0};
@@ -780,7 +785,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tmem_st4(lane_addr + e_col0 + buf * 4, mw[0], mw[1], mw[2], mw[3]);
           // the packed stage has been consumed
           mbar_arrive(smem_u32(&bar_r_empty[rslot]));
-          if (INSTR) { const long long tc1 = clock64(); t_deq += tc1 - tc0; tc0 = tc1; }
           // the slot's token window: rows of the resident x half-tiles, other slots' rows zeroed
           {
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
@@ -798,12 +802,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               *reinterpret_cast<uint4*>(my_win + (size_t)idx * 16) = v;
             }
           }
-          if (INSTR) { const long long tc1 = clock64(); t_copy += tc1 - tc0; tc0 = tc1; }
           fence_proxy_async();
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_a_ready[buf]));
-          if (INSTR) t_sync += clock64() - tc0;
         }
         // this warpgroup no longer reads the unit's x half-tiles
         mbar_arrive(smem_u32(&bar_x_empty[xslot0]));
@@ -811,79 +813,96 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
 
       // ---------------- epilogue of this fragment ----------------
-      const long long te0 = INSTR ? clock64() : 0;
-      const long long accf0 = t_accf;
-      mbar_wait_t<INSTR>(smem_u32(bar_acc_full), pacc, abort_flag, p.status, t_accf);
+      // A fragment that does not cover its whole tile settles the tile with the other
+      // fragments through two counters: `ticket` (claimed while this fragment's last MMAs
+      // drain) and `parked`.  The holder of the last ticket never parks anything: it waits
+      // until the others have parked (they hold earlier tickets, so they are already in their
+      // epilogues and depend on nothing), then adds their partials to its own accumulators in
+      // fragment order, straight from registers.  Every other fragment parks its partial and
+      // leaves with a single fire-and-forget release increment.
+      const bool full_tile = (ku0 == 0 && ku1 == KU);
+      int c_first = 0, nfrag = 1, ticket = 0;
+      if (!full_tile) {
+        c_first = cta_of_unit((long long)tile * KU, p.grid, p.total_units);
+        nfrag = cta_of_unit((long long)(tile + 1) * KU - 1, p.grid, p.total_units) - c_first + 1;
+        if (ep_tid == 0) ticket = atomicAdd(&p.counters[2 * tile], 1);
+      }
+      mbar_wait(smem_u32(bar_acc_full), pacc, abort_flag, p.status);
       pacc ^= 1;
       tc_fence_after();
-      const bool full_tile = (ku0 == 0 && ku1 == KU);
+      if (INSTR && ep_tid == 0 && ku1 - ku0 == u_end - u) tl[5] = globaltimer();
+      bool last = false;
+      if (!full_tile) {
+        if (ep_tid == 0) {
+          const int is_last = (ticket == nfrag - 1) ? 1 : 0;
+          if (is_last) {
+            // bounded wait for the earlier ticket holders' partials
+            unsigned long long t0 = 0;
+            for (uint32_t it = 0;; ++it) {
+              int parked;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];"
+                           : "=r"(parked)
+                           : "l"(p.counters + 2 * tile + 1)
+                           : "memory");
+              if (parked >= nfrag - 1 || *abort_flag) break;
+              __nanosleep(64);
+              if ((it & 63u) == 63u) {
+                const unsigned long long now = globaltimer();
+                if (t0 == 0) {
+                  t0 = now;
+                } else if (now - t0 > kTimeoutNs) {
+                  *abort_flag = 1;
+                  atomicCAS(p.status, 0, (int)DZ_ERR_TIMEOUT);
+                  break;
+                }
+              }
+            }
+            // the tile is settled once this fragment has written it: counters back to zero
+            p.counters[2 * tile] = 0;
+            p.counters[2 * tile + 1] = 0;
+          }
+          s_last = is_last;
+        }
+        named_bar_sync(1, 128 * kNumWG);
+        last = s_last != 0;
+      }
       float* my_partial = p.partials +
                           ((size_t)cta * 2 + (cta_first_fragment ? 0 : 1)) * ((size_t)p.cols * 128);
       for (int c = wg; c < p.cols / 16; c += kNumWG) {
-        uint32_t v[16], d[16];
-        tmem_ld16(lane_addr + c * 16, v);
-        if (nwin > 0) tmem_ld16(lane_addr + p.dcols + c * 16, d);
-        tmem_wait_ld();
-        if (nwin > 0) {
-          if (c != wg) {   // second chunk of a wide token block: its scales are fetched here
+        if (nwin > 0 && c != wg) {   // second chunk of a wide token block: its scales are fetched here
 #pragma unroll
-            for (int i = 0; i < 8; ++i) csc[i] = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int slot = s_slot[c * 16 + i];
-              uint32_t sv = 0;
-              if (slot >= 0)
-                sv = *reinterpret_cast<const unsigned short*>(p.scales + (size_t)slot * p.sstride +
-                                                              (size_t)(n0 + r) * 2);
-              csc[i >> 1] |= sv << (16 * (i & 1));
-            }
-          }
+          for (int i = 0; i < 8; ++i) csc[i] = 0;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float sc = __half2float(__ushort_as_half((unsigned short)(csc[i >> 1] >> (16 * (i & 1)))));
-            v[i] = __float_as_uint(fmaf(sc, __uint_as_float(d[i]), __uint_as_float(v[i])));
+            const int slot = s_slot[c * 16 + i];
+            uint32_t sv = 0;
+            if (slot >= 0)
+              sv = *reinterpret_cast<const unsigned short*>(p.scales + (size_t)slot * p.sstride +
+                                                            (size_t)(n0 + r) * 2);
+            csc[i >> 1] |= sv << (16 * (i & 1));
           }
-          tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
         }
-        if (full_tile) {
+        // eight columns at a time keep the epilogue's register needs below the main loop's
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int prow = p.row0 + c * 16 + i;
-            if (prow < p.M) {
-              const int tok = perm ? perm[prow] : prow;
-              store_out<DT>(p.y, (size_t)tok * p.N + n0 + r, __uint_as_float(v[i]));
+        for (int hb = 0; hb < 2; ++hb) {
+          const int col = c * 16 + hb * 8;
+          uint32_t v[8], d[8];
+          tmem_ld8(lane_addr + col, v);
+          if (nwin > 0) tmem_ld8(lane_addr + p.dcols + col, d);
+          tmem_wait_ld();
+          if (nwin > 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t pair = csc[hb * 4 + (i >> 1)];
+              const float sc = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (i & 1)))));
+              v[i] = __float_as_uint(fmaf(sc, __uint_as_float(d[i]), __uint_as_float(v[i])));
             }
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            __stcg(my_partial + (size_t)(c * 16 + i) * 128 + r, __uint_as_float(v[i]));
-        }
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(smem_u32(bar_acc_empty));
-
-      if (!full_tile) {
-        // fragments of this tile, in CTA order
-        const int c_first = cta_of_unit((long long)tile * KU, p.grid, p.total_units);
-        const int c_last = cta_of_unit((long long)(tile + 1) * KU - 1, p.grid, p.total_units);
-        const int nfrag = c_last - c_first + 1;
-        // release pattern: every thread's partial stores happen before the
-        // barrier; one thread then fences at device scope and publishes
-        named_bar_sync(1, 128 * kNumWG);
-        if (ep_tid == 0) {
-          __threadfence();
-          const int old = atomicAdd(&p.counters[tile], 1);
-          s_last = (old == nfrag - 1) ? 1 : 0;
-        }
-        named_bar_sync(1, 128 * kNumWG);
-        if (s_last) {
-          __threadfence();
-          // 8 columns x 2 fragments per pass: 16 independent L2 loads in
-          // flight (a column-at-a-time loop is a chain of L2 latencies); the
-          // additions stay in fragment order
-          for (int cb = wg * 8; cb < p.cols; cb += kNumWG * 8) {
+          if (last) {
+            // sum over the tile's fragments in CTA order, this fragment's accumulators taking
+            // their own place in that order; 8 columns x 2 fragments per pass keep 16
+            // independent L2 loads in flight
+            const int my_f = cta - c_first;
             float sum[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) sum[i] = 0.f;
@@ -892,53 +911,62 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
               for (int ff = 0; ff < 2; ++ff) {
                 const int f = f0 + ff;
-                if (f < nfrag) {
+                if (f < nfrag && f != my_f) {
                   const int cc = c_first + f;
                   const int cu0 = (int)((long long)cc * U / p.grid);
                   const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
                   const float* src =
-                      p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)cb * 128 + r;
+                      p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)col * 128 + r;
 #pragma unroll
                   for (int i = 0; i < 8; ++i) part[ff][i] = __ldcg(src + i * 128);
                 } else {
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) part[ff][i] = 0.f;
+                  for (int i = 0; i < 8; ++i)
+                    part[ff][i] = (f == my_f) ? __uint_as_float(v[i]) : 0.f;
                 }
               }
 #pragma unroll
               for (int ff = 0; ff < 2; ++ff)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) sum[i] += part[ff][i];
+                for (int i = 0; i < 8; ++i)
+                  if (f0 + ff < nfrag) sum[i] += part[ff][i];
             }
 #pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __float_as_uint(sum[i]);
+          }
+          if (full_tile || last) {
+#pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const int prow = p.row0 + cb + i;
+              const int prow = p.row0 + col + i;
               if (prow < p.M) {
                 const int tok = perm ? perm[prow] : prow;
-                store_out<DT>(p.y, (size_t)tok * p.N + n0 + r, sum[i]);
+                store_out<DT>(p.y, (size_t)tok * p.N + n0 + r, __uint_as_float(v[i]));
               }
             }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              __stcg(my_partial + (size_t)(col + i) * 128 + r, __uint_as_float(v[i]));
           }
-          if (ep_tid == 0) p.counters[tile] = 0;
         }
+        if (nwin > 0) tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(bar_acc_empty));
+
+      if (!full_tile && !last) {
+        // release pattern: every thread's partial stores happen before the barrier; one
+        // thread then publishes with a device-scope release
         named_bar_sync(1, 128 * kNumWG);
+        if (ep_tid == 0)
+          asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.counters + 2 * tile + 1)
+                       : "memory");
       }
       cta_first_fragment = false;
       u += ku1 - ku0;
-      if (INSTR) t_epi += (clock64() - te0) - (t_accf - accf0);
     }
-    if (INSTR && ep_tid == 0) {
-      unsigned long long* st = reinterpret_cast<unsigned long long*>(p.status + 16);
-      atomicAdd(st + 6, (unsigned long long)(clock64() - t_start));
-      atomicAdd(st + 7, (unsigned long long)t_rfull);
-      atomicAdd(st + 8, (unsigned long long)t_afree);
-      atomicAdd(st + 9, (unsigned long long)t_xfull);
-      atomicAdd(st + 10, (unsigned long long)t_accf);
-      atomicAdd(st + 11, (unsigned long long)t_deq);
-      atomicAdd(st + 12, (unsigned long long)t_copy);
-      atomicAdd(st + 13, (unsigned long long)t_sync);
-      atomicAdd(st + 14, (unsigned long long)t_epi);
-    }
+    if (INSTR && ep_tid == 0) tl[6] = globaltimer();
   }
 
   // ---- teardown ----
@@ -957,6 +985,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                  "n"(kTmemCols)
                  : "memory");
   }
+  if (INSTR && threadIdx.x == 0) tl[7] = globaltimer();
 }
 
 // gathers x rows into sorted order: xs[p] = x[perm[p]]
@@ -1070,7 +1099,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   DZ_CUDA_OK(cudaGetDevice(&dev));
   DeviceInfo& di = device_info(dev);
   if (di.sms == 0) DZ_CUDA_OK(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
-  if (a.N / kTileN > (int)(kWsCountersBytes / 4)) return DZ_ERR_TOO_LARGE;
+  if (a.N / kTileN > (int)(kWsCountersBytes / 8)) return DZ_ERR_TOO_LARGE;
 
   uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
   const bool sorted = base_only || a.tokens_sorted != 0;
