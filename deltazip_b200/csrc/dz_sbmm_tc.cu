@@ -28,12 +28,14 @@
 // the same class, so the summation order of every output is fixed no matter how
 // the issuers interleave.
 //
-// Work split.  (tile, k-unit of 128) pairs are divided evenly over one CTA per
-// SM ("stream-K"): a CTA walks a contiguous unit range, which may cover the
-// tail of one tile, whole tiles and the head of another.  A fragment that does
-// not cover a whole tile parks its fp32 partial in the workspace; the last
-// fragment of a tile to finish (a per-tile counter) adds the partials in fixed
-// order, so results do not depend on timing.
+// Work split.  (tile, k-unit of 128) pairs are divided over one CTA per SM
+// ("stream-K", with a tile's epilogue counted as one more unit): a CTA walks a
+// contiguous unit range, which may cover the tail of one tile, whole tiles and
+// the head of another.  The fragments of a split tile settle it through two
+// per-tile counters: each claims a ticket; all but the holder of the last
+// ticket park their fp32 partial in the workspace; the last holder adds the
+// parked partials and its own accumulators in CTA order, so results do not
+// depend on timing.
 //
 // Every mbarrier wait is bounded: on a timeout the CTA records DZ_ERR_TIMEOUT,
 // raises an abort flag that turns every later wait into a no-op, runs its
@@ -71,6 +73,7 @@ constexpr int kTmemCols = 512;
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
 constexpr int kMaxCtas = 160;
 constexpr int kSmemBudget = 216 * 1024;
+constexpr int kEpilogueUnits = 1;               // cost of a tile's epilogue in k-units (work split)
 constexpr int kPrefetchTiles = 8;               // W half-tiles prefetched to L2 in the prologue
 
 // TMEM columns: D_base [0, dcols), D_delta [dcols, 2 dcols), then 32 columns of
@@ -84,7 +87,7 @@ struct Params {
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
   int base_only, tokens_sorted;
   int debug;
-  int grid, total_units;
+  int grid, total_units, epi_units;   // total_units counts virtual units
   int w_stages, x_stages, r_per_class, xb_bytes;
   int nclass, dcols;
   const uint8_t* qweight;
@@ -377,10 +380,22 @@ __device__ __forceinline__ void expand_word2(uint32_t w, uint32_t* o) {
   }
 }
 
-// CTA that owns unit u when `total` units are split evenly over `grid` CTAs
-// (CTA c owns [c*total/grid, (c+1)*total/grid)).
-__device__ __forceinline__ int cta_of_unit(long long u, int grid, int total) {
-  return (int)(((u + 1) * grid - 1) / total);
+// Work split.  Every tile is given KU + E "virtual" units: its KU k-units followed by E units
+// that stand for the cost of the tile's epilogue, and the virtual units are divided evenly
+// over the CTAs (CTA c owns [c*V/grid, (c+1)*V/grid)).  A CTA that finishes a tile in the middle
+// of its range is thereby given fewer k-units than one that does not.
+// First real unit (tile * KU + ku) of CTA c:
+// (32-bit arithmetic: the host refuses shapes with V * grid >= 2^31)
+__device__ __forceinline__ int split_begin(int c, int grid, int KU, int E, int V) {
+  const int v = (int)((unsigned)c * (unsigned)V / (unsigned)grid);
+  const int tile = v / (KU + E);
+  const int off = v - tile * (KU + E);
+  return tile * KU + min(off, KU);
+}
+// CTA that owns k-unit ku of `tile`
+__device__ __forceinline__ int split_owner(int tile, int ku, int grid, int KU, int E, int V) {
+  const unsigned v = (unsigned)(tile * (KU + E) + ku);
+  return (int)(((v + 1u) * (unsigned)grid - 1u) / (unsigned)V);
 }
 
 struct WinS {
@@ -449,9 +464,9 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   // ---- this CTA's unit range ----
   const int cta = blockIdx.x;
-  const long long U = p.total_units;
-  const int u_begin = (int)((long long)cta * U / p.grid);
-  const int u_end = (int)((long long)(cta + 1) * U / p.grid);
+  const int U = p.total_units;   // virtual units
+  const int u_begin = split_begin(cta, p.grid, p.num_kunits, p.epi_units, U);
+  const int u_end = split_begin(cta + 1, p.grid, p.num_kunits, p.epi_units, U);
   const int KU = p.num_kunits;
 
   // ---- part of the prologue that reads nothing an earlier kernel may still be writing ----
@@ -481,7 +496,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // pull the first W tiles of this CTA's range towards L2 (a prefetch consumes no data, so it
     // is safe whatever the predecessor writes)
     int issued = 0;
-    for (int u = u_begin; u < u_end && issued < kPrefetchTiles && !(p.debug & 1); ++u) {
+    for (int u = u_begin; u < u_end && issued < kPrefetchTiles; ++u) {
       const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
       const int nhalf = min(2, (p.K - k0) / kBlockK);
       for (int h = 0; h < nhalf; ++h, ++issued)
@@ -722,23 +737,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int tile = u / KU, ku0 = u % KU;
       const int ku1 = min(KU, ku0 + (u_end - u));
       const int n0 = tile * kTileN;
-      // D_delta holds sums of (code - zero) * x; the per-channel scale of each
-      // column's slot is applied in the epilogue.  The scales depend only on
-      // (tile, column), so they are fetched now and arrive during the main loop.
-      uint32_t csc[8];   // fp16 bit patterns of column chunk `wg`, two columns per word
-#pragma unroll
-      for (int i = 0; i < 8; ++i) csc[i] = 0;
-      if (nwin > 0 && wg < p.cols / 16) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int slot = s_slot[wg * 16 + i];
-          uint32_t v = 0;
-          if (slot >= 0)
-            v = *reinterpret_cast<const unsigned short*>(p.scales + (size_t)slot * p.sstride +
-                                                         (size_t)(n0 + r) * 2);
-          csc[i >> 1] |= v << (16 * (i & 1));
-        }
-      }
       for (int ku = ku0; ku < ku1 && active; ++ku) {
         const int k0 = ku * kUnitK;
         const int nhalf = min(2, (p.K - k0) / kBlockK);
@@ -823,9 +821,26 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const bool full_tile = (ku0 == 0 && ku1 == KU);
       int c_first = 0, nfrag = 1, ticket = 0;
       if (!full_tile) {
-        c_first = cta_of_unit((long long)tile * KU, p.grid, p.total_units);
-        nfrag = cta_of_unit((long long)(tile + 1) * KU - 1, p.grid, p.total_units) - c_first + 1;
+        c_first = split_owner(tile, 0, p.grid, KU, p.epi_units, U);
+        nfrag = split_owner(tile, KU - 1, p.grid, KU, p.epi_units, U) - c_first + 1;
         if (ep_tid == 0) ticket = atomicAdd(&p.counters[2 * tile], 1);
+      }
+      // D_delta holds sums of (code - zero) * x; the per-channel scale of each
+      // column's slot is applied here.  The scales are requested before the wait for the
+      // fragment's last MMAs, so they arrive while those drain.
+      uint32_t csc[8];   // fp16 bit patterns of column chunk `wg`, two columns per word
+#pragma unroll
+      for (int i = 0; i < 8; ++i) csc[i] = 0;
+      if (nwin > 0 && wg < p.cols / 16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int slot = s_slot[wg * 16 + i];
+          uint32_t v = 0;
+          if (slot >= 0)
+            v = *reinterpret_cast<const unsigned short*>(p.scales + (size_t)slot * p.sstride +
+                                                         (size_t)(n0 + r) * 2);
+          csc[i >> 1] |= v << (16 * (i & 1));
+        }
       }
       mbar_wait(smem_u32(bar_acc_full), pacc, abort_flag, p.status);
       pacc ^= 1;
@@ -913,7 +928,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int f = f0 + ff;
                 if (f < nfrag && f != my_f) {
                   const int cc = c_first + f;
-                  const int cu0 = (int)((long long)cc * U / p.grid);
+                  const int cu0 = split_begin(cc, p.grid, KU, p.epi_units, U);
                   const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
                   const float* src =
                       p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)col * 128 + r;
@@ -1125,8 +1140,10 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.base_only = base_only ? 1 : 0;
   { const char* e = getenv("DZ_DEBUG"); p.debug = e ? atoi(e) : 0; }
   p.tokens_sorted = sorted ? 1 : 0;
-  p.total_units = p.num_tiles * p.num_kunits;
-  p.grid = min(min(di.sms, kMaxCtas), p.total_units);
+  p.epi_units = kEpilogueUnits;
+  p.total_units = p.num_tiles * (p.num_kunits + p.epi_units);
+  p.grid = min(min(di.sms, kMaxCtas), p.num_tiles * p.num_kunits);
+  if ((long long)(p.total_units + 1) * p.grid >= (1ll << 31)) return DZ_ERR_TOO_LARGE;
   p.qweight = (const uint8_t*)a.qweight;
   p.meta = (const uint8_t*)a.meta;
   p.scales = (const uint8_t*)a.scales;
