@@ -148,8 +148,13 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    car = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+        if args.allreduce == "custom":
+            # the library's peer-memory all-reduce for the row-parallel outputs
+            from deltazip_b200 import custom_all_reduce
+            car = custom_all_reduce.init_custom_ar(rank, world)
     tp = world
     L = _lib.lib()
 
@@ -188,15 +193,30 @@ def run_ours(args):
             calls.append((a, rowp, y_dev[n]))
             step_bytes += algorithmic_bytes(TOKENS, n, k, active, BITS)
 
+    stage_ptr, stage_len = ctypes.c_void_p(), ctypes.c_size_t()
+
     def step_device():
         n_launch = 0
         for a, rowp, y in calls:
+            reduce = rowp and tp > 1
+            if reduce and car is not None:
+                # the SBMM writes its partial output straight into the staging buffer of the
+                # all-reduce that follows (buffers alternate from call to call)
+                L.dz_allreduce_staging(car._ctx, ctypes.byref(stage_ptr), ctypes.byref(stage_len))
+                a.y = stage_ptr.value
             rc = L.dz_sbmm(ctypes.byref(a), stream)
             if rc:
                 _lib.check(rc, "dz_sbmm")
             n_launch += 1
-            if rowp and tp > 1:
-                dist.all_reduce(y)
+            if reduce:
+                if car is not None:
+                    rc = L.dz_allreduce_run(car._ctx, stage_ptr, y.data_ptr(), y.numel(),
+                                            _lib.DZ_DTYPE_F16, stream)
+                    if rc:
+                        _lib.check(rc, "dz_allreduce_run")
+                    n_launch += 1
+                else:
+                    dist.all_reduce(y)
         return n_launch
 
     def barrier():
@@ -230,7 +250,8 @@ def run_ours(args):
     kev0, kev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     kev0.record()
-    for a, _, _ in calls:
+    for a, _, y in calls:
+        a.y = y.data_ptr()
         L.dz_sbmm(ctypes.byref(a), stream)
     kev1.record()
     torch.cuda.synchronize()
@@ -245,9 +266,14 @@ def run_ours(args):
         for entry in layers:
             for name, n, k, rowp in projs:
                 e = entry[name]
-                y = ops.sbmm(xd[k], e["q"], e["s"], e["m"], seg, e["w"], out=y_dev[n], bits=BITS)
-                if rowp and tp > 1:
-                    dist.all_reduce(y)
+                reduce = rowp and tp > 1
+                out = car.staging_like((TOKENS, n), torch.float16) if (reduce and car) else y_dev[n]
+                y = ops.sbmm(xd[k], e["q"], e["s"], e["m"], seg, e["w"], out=out, bits=BITS)
+                if reduce:
+                    if car is not None:
+                        y = car.all_reduce(y, out=y_dev[n])
+                    else:
+                        dist.all_reduce(y)
         y_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -287,6 +313,8 @@ def run_ours(args):
                 "tokens": TOKENS, "deltas": NUM_DELTAS, "active_deltas": active, "bits": BITS,
                 "layers": args.layers, "sbmm_calls_per_step": n_calls,
                 "parallelism": f"tp{world}",
+                "allreduce": ("peer-memory one-shot (dz_allreduce_run)" if car is not None
+                              else ("nccl" if world > 1 else "none")),
                 "l2": "inputs larger than L2: each step streams %.1f GB of distinct weights"
                       % (step_bytes * 1e-9),
             },
@@ -310,6 +338,12 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
         print(json.dumps(line), flush=True)
     if world > 1:
+        if car is not None:
+            st = car.status()
+            if st:
+                raise SystemExit(f"peer-memory all-reduce reported status {st}")
+            from deltazip_b200 import custom_all_reduce
+            custom_all_reduce.destroy_custom_ar()
         dist.destroy_process_group()
 
 
@@ -431,6 +465,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="decoder layers to instantiate (32 = the benchmark; fewer only for profiling captures)")
+    ap.add_argument("--allreduce", default="custom", choices=["custom", "nccl"],
+                    help="N>1: all-reduce after the row-parallel layers (library peer-memory kernel or NCCL)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

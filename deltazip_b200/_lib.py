@@ -27,6 +27,7 @@ DZ_ERR_TOO_LARGE = 11
 
 DZ_DTYPE_F16 = 0
 DZ_DTYPE_BF16 = 1
+DZ_DTYPE_F32 = 2
 DZ_INDEX_I32 = 0
 DZ_INDEX_I64 = 1
 
@@ -78,6 +79,14 @@ _SIGNATURES = {
     "dz_slot_upload": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "dz_slot_reset": (c_int, [c_void_p, c_size_t, c_void_p]),
     "dz_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
+    "dz_allreduce_region_bytes": (c_size_t, [c_size_t]),
+    "dz_allreduce_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_size_t]),
+    "dz_allreduce_export": (c_int, [c_void_p, c_void_p]),
+    "dz_allreduce_connect": (c_int, [c_void_p, c_void_p]),
+    "dz_allreduce_staging": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),
+    "dz_allreduce_run": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "dz_allreduce_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "dz_allreduce_destroy": (c_int, [c_void_p]),
 }
 
 

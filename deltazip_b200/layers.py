@@ -19,6 +19,7 @@ import torch.nn as nn
 
 from . import ops
 from .config import DeltaConfig
+from .custom_all_reduce import get_handle as get_custom_ar_handle
 from .parallel_state import (get_tensor_model_parallel_rank, get_tensor_model_parallel_world_size,
                              shard_range, tensor_model_parallel_all_gather,
                              tensor_model_parallel_all_reduce)
@@ -207,15 +208,20 @@ class BaseLayerWithDelta(nn.Module):
         self.segments = segments
 
     # -- compute -------------------------------------------------------------
-    def apply_weights(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def apply_weights(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if bias is not None:
             raise ValueError("delta layers do not support bias yet.")
         w = self.base_layer.linear_weights["weight"]
         if self.segments is not None:
             return ops.sbmm(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
-                            self.segments, w, bits=self.bits)
-        return ops.apply_delta(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
-                               self.indices[: self.indices_len[0]], w)
+                            self.segments, w, out=out, bits=self.bits)
+        y = ops.apply_delta(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
+                            self.indices[: self.indices_len[0]], w)
+        if out is not None:
+            out.copy_(y.reshape(out.shape))
+            return out
+        return y
 
     @property
     def linear_weights(self):
@@ -273,9 +279,21 @@ class RowParallelLinearWithDelta(BaseLayerWithDelta):
             x = input_
         else:
             x = input_[..., base.shard[0]:base.shard[1]].contiguous()
-        out = self.apply_weights(x)
-        if base.reduce_results and base.tp_size > 1:
+        reduce = base.reduce_results and base.tp_size > 1
+        staged = None
+        if reduce:
+            # produce the partial output directly in peer-visible memory when the
+            # peer-memory all-reduce will take it (saves its copy-in)
+            handle = get_custom_ar_handle()
+            rows = x.numel() // x.shape[-1]
+            n = base.linear_weights["weight"].shape[0]
+            if handle is not None and 0 < rows * n * x.element_size() <= handle.max_size and \
+                    (rows * n * x.element_size()) % 16 == 0:
+                staged = handle.staging_like((rows, n), x.dtype)
+        out = self.apply_weights(x, out=staged)
+        if reduce:
             out = tensor_model_parallel_all_reduce(out)
+            out = out.reshape(*x.shape[:-1], out.shape[-1])
         return out, None
 
     @classmethod

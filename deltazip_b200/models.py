@@ -83,6 +83,31 @@ class DeltaLayerWeights:
         return self
 
 
+def shard_gptq_tensors(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, bits: int,
+                       parallel: str, tp_rank: int, tp_size: int
+                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """This rank's shard of one module's GPTQ-layout tensors (qweight int32 [K*bits/32, N],
+    qzeros int32 [1, N*bits/32], scales fp16 [1, N]).
+
+    "column": the output features are cut at whole 128-row tiles (qweight columns, scales and
+    packed zero points sliced); "row": the input features are cut at whole 64-wide blocks
+    (qweight rows sliced; 2:4 groups and the per-output-channel scales are untouched).  The
+    same cuts as the base layers (layers.py) and as the reference's per-rank files
+    (serving/vllm/delta/models.py:239-258, written by tools/optimize_io.py:9-66)."""
+    from .parallel_state import shard_range
+    per = 32 // bits
+    k = qweight.shape[0] * per
+    n = qweight.shape[1]
+    if parallel == "column":
+        lo, hi = shard_range(n, 128, tp_rank, tp_size)
+        return (qweight[:, lo:hi].contiguous(), qzeros[:, lo // per:hi // per].contiguous(),
+                scales[:, lo:hi].contiguous())
+    if parallel == "row":
+        lo, hi = shard_range(k, 64, tp_rank, tp_size)
+        return qweight[lo // per:hi // per].contiguous(), qzeros, scales
+    raise ValueError(f"unknown parallel mode {parallel!r}")
+
+
 class DeltaModel:
     """One fine-tuned variant: module name -> DeltaLayerWeights."""
 

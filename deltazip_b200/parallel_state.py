@@ -3,7 +3,8 @@
 Role of serving/vllm/model_executor/parallel_utils/parallel_state.py:22-87 and
 communication_op.py:17-105 for this path: one tensor-parallel group spanning
 all ranks (one process per GPU, torch.distributed; NCCL on GPUs, gloo in the
-CPU tests), all-reduce after row-parallel layers, all-gather for
+CPU tests), all-reduce after row-parallel layers (the library's peer-memory
+all-reduce when the message qualifies, else the backend's), all-gather for
 gather_output column layers.
 """
 from __future__ import annotations
@@ -18,8 +19,11 @@ _TP_SIZE = 1
 _TP_RANK = 0
 
 
-def initialize_model_parallel(tensor_model_parallel_size: int = 1) -> None:
-    """All ranks of the default group form the tensor-parallel group."""
+def initialize_model_parallel(tensor_model_parallel_size: int = 1,
+                              disable_custom_all_reduce: bool = False) -> None:
+    """All ranks of the default group form the tensor-parallel group.  On an NCCL group of up
+    to 8 ranks the peer-memory all-reduce is set up too (collective call) unless disabled, as
+    the reference does in its worker (serving/vllm/worker/worker.py: init_custom_ar)."""
     global _TP_GROUP, _TP_SIZE, _TP_RANK
     if tensor_model_parallel_size == 1 or not dist.is_initialized():
         _TP_GROUP, _TP_SIZE, _TP_RANK = None, 1, 0
@@ -30,10 +34,15 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1) -> None:
     _TP_GROUP = dist.group.WORLD
     _TP_SIZE = world
     _TP_RANK = dist.get_rank()
+    if not disable_custom_all_reduce and dist.get_backend() == "nccl" and world <= 8:
+        from . import custom_all_reduce
+        custom_all_reduce.init_custom_ar(_TP_RANK, world, group=_TP_GROUP)
 
 
 def destroy_model_parallel() -> None:
     global _TP_GROUP, _TP_SIZE, _TP_RANK
+    from . import custom_all_reduce
+    custom_all_reduce.destroy_custom_ar()
     _TP_GROUP, _TP_SIZE, _TP_RANK = None, 1, 0
 
 
@@ -46,9 +55,14 @@ def get_tensor_model_parallel_rank() -> int:
 
 
 def tensor_model_parallel_all_reduce(x: torch.Tensor) -> torch.Tensor:
-    """In-place sum over the tensor-parallel ranks (no-op for one rank)."""
+    """Sum over the tensor-parallel ranks (no-op for one rank).  May or may not work in
+    place: always use the return value (same contract as communication_op.py:17-40)."""
     if _TP_SIZE == 1:
         return x
+    from .custom_all_reduce import custom_all_reduce
+    out = custom_all_reduce(x)
+    if out is not None:
+        return out
     dist.all_reduce(x, group=_TP_GROUP)
     return x
 

@@ -37,7 +37,7 @@ typedef enum {
   DZ_ERR_TOO_LARGE = 11     /* size beyond a fixed maximum of the entry point   */
 } dz_status;
 
-enum { DZ_DTYPE_F16 = 0, DZ_DTYPE_BF16 = 1 };
+enum { DZ_DTYPE_F16 = 0, DZ_DTYPE_BF16 = 1, DZ_DTYPE_F32 = 2 /* all-reduce only */ };
 enum { DZ_INDEX_I32 = 0, DZ_INDEX_I64 = 1 };
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -179,6 +179,41 @@ int dz_delta_embedding(const int64_t* token_ids, const void* indices, int index_
 int dz_slot_upload(void* dst_device, const void* src_pinned_host, size_t bytes,
                    int zero_first, void* copy_stream);
 int dz_slot_reset(void* dst_device, size_t bytes, void* stream);
+
+/*
+ * All-reduce (sum) of the row-parallel layers' partial outputs over peer memory,
+ * one process per GPU on one node.  Replaces the reference's CustomAllreduce
+ * (serving/vllm/model_executor/parallel_utils/custom_all_reduce.py:187-262,
+ * serving/csrc/custom_all_reduce.cuh; called from communication_op.py:17-40
+ * after serving/vllm/delta/layers_marlin.py:583-584).
+ *
+ *   create   allocates this rank's region (flags + two staging buffers) with
+ *            cudaMalloc -- set-up time, never on the hot path;
+ *   export   writes the region's 64-byte CUDA IPC handle; the caller exchanges
+ *            the handles of all ranks by any means (torch.distributed here);
+ *   connect  takes world * 64 bytes of handles in rank order and maps the peers;
+ *   staging  returns where the NEXT run's input may be produced in place (the
+ *            row-parallel SBMM writes y there, which saves the copy-in);
+ *   run      enqueues one kernel on `stream`: out = sum over ranks of in, fp32
+ *            accumulation in rank order (bit-identical on every rank); count
+ *            elements of DZ_DTYPE_*, count * size <= max_bytes and a multiple
+ *            of 16, pointers 16-byte aligned; `out` may be any device buffer.
+ *            Every rank must issue the same sequence of runs.  Not capturable
+ *            into a CUDA graph (the call's epoch is a kernel argument).
+ *   status   reads the region's status word: DZ_ERR_TIMEOUT when a peer's data
+ *            did not arrive within one second (the kernel then returns without
+ *            reducing instead of waiting forever).
+ */
+typedef struct dz_allreduce_ctx dz_allreduce_ctx;
+size_t dz_allreduce_region_bytes(size_t max_bytes);
+int dz_allreduce_create(dz_allreduce_ctx** ctx, int rank, int world, size_t max_bytes);
+int dz_allreduce_export(dz_allreduce_ctx* ctx, unsigned char* handle64);
+int dz_allreduce_connect(dz_allreduce_ctx* ctx, const unsigned char* handles);
+int dz_allreduce_staging(dz_allreduce_ctx* ctx, void** ptr, size_t* bytes);
+int dz_allreduce_run(dz_allreduce_ctx* ctx, const void* in, void* out, int64_t count,
+                     int dtype, void* stream);
+int dz_allreduce_status(dz_allreduce_ctx* ctx, int* status);
+int dz_allreduce_destroy(dz_allreduce_ctx* ctx);
 
 /* Reads and clears a device status word (synchronises `stream`). */
 int dz_read_status(int* status_word, void* stream, int* host_out);

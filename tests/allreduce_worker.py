@@ -1,0 +1,117 @@
+"""Worker of tests/test_gpu_allreduce.py: one process per GPU under torch.distributed.run.
+
+Checks the peer-memory all-reduce against a rank-order fp32 sum of the gathered inputs
+(bit-exact), across sizes and dtypes, through the staging (zero-copy) path, over many
+back-to-back calls, through a tensor-parallel row-parallel delta layer, and finally the bounded
+wait: one rank issues a call that its peers never join and must get DZ_ERR_TIMEOUT back, with
+its CUDA context still usable.
+"""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch
+import torch.distributed as dist
+
+from deltazip_b200 import _lib, custom_all_reduce, layers, ops, parallel_state, synth
+from deltazip_b200.config import DeltaConfig
+from deltazip_b200.models import shard_gptq_tensors
+
+
+def expected_sum(parts, dtype):
+    acc = torch.zeros_like(parts[0], dtype=torch.float32)
+    for p in parts:                       # rank order, fp32, one rounding at the end
+        acc = acc + p.float()
+    return acc.to(dtype)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    parallel_state.initialize_model_parallel(world)
+    h = custom_all_reduce.get_handle()
+    assert h is not None, "custom all-reduce handle was not created"
+
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    # --- sizes x dtypes, out of place, bit-exact against the rank-order fp32 sum ---
+    for dtype in (torch.float16, torch.bfloat16, torch.float32):
+        for numel in (8, 4096, 64 * 4096, 1000 * 8, 2 * 1024 * 1024):
+            x = torch.randn(numel, device=dev, dtype=torch.float32, generator=g).to(dtype)
+            parts = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(parts, x)
+            want = expected_sum(parts, dtype)
+            assert h.should_custom_ar(x)
+            got = custom_all_reduce.custom_all_reduce(x)
+            assert got is not None and got.data_ptr() != x.data_ptr()
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), (dtype, numel, (got.float() - want.float()).abs().max())
+            outs = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(outs, got)
+            assert all(torch.equal(o, outs[0]) for o in outs), "ranks disagree"
+    # --- messages that do not qualify fall back (None) ---
+    assert custom_all_reduce.custom_all_reduce(torch.zeros(3, device=dev, dtype=torch.float16)) is None
+    big = torch.zeros(h.max_size // 2 + 8, device=dev, dtype=torch.float16)
+    assert custom_all_reduce.custom_all_reduce(big) is None
+    y = parallel_state.tensor_model_parallel_all_reduce(torch.ones(3, device=dev))
+    assert torch.equal(y, torch.full((3,), float(world), device=dev))
+
+    # --- staging path + many back-to-back calls with changing data (buffer alternation) ---
+    shape = (64, 4096)
+    for it in range(200):
+        st = h.staging_like(shape, torch.float16)
+        st.copy_(torch.full(shape, float(rank + 1 + (it % 7)), device=dev, dtype=torch.float16))
+        out = h.all_reduce(st)
+        if it % 50 == 49 or it < 4:
+            want = float(sum(r + 1 + (it % 7) for r in range(world)))
+            assert torch.equal(out, torch.full(shape, want, device=dev, dtype=torch.float16)), it
+    torch.cuda.synchronize()
+    assert h.status() == 0
+
+    # --- row-parallel delta layer under tensor parallelism vs the unsharded layer ---
+    n, k, slots, bits, m = 512, 1024, 4, 4, 48
+    gen = torch.Generator(device=dev).manual_seed(7)          # same data on every rank
+    w = (torch.randn(n, k, generator=gen, device=dev) * 0.02).half()
+    x = torch.randn(m, k, generator=gen, device=dev).half()
+    idx = torch.sort(torch.randint(-1, slots, (m,), generator=gen, device=dev))[0]
+    full = ops.alloc_slots(slots, n, k, bits, dev)
+    lo, hi = parallel_state.shard_range(k, 64, rank, world)
+    base = layers.RowParallelLinear(k, n, device=dev)
+    base.weight.data.copy_(w[:, lo:hi])
+    layer = layers.RowParallelLinearWithDelta(base)
+    layer.create_delta_weights(slots, DeltaConfig(max_deltas=slots, max_bitwidth=bits))
+    for d in range(slots):
+        delta = torch.randn((n, k), generator=gen, device=dev) * 1e-2
+        qw, qz, sc = synth.compress_delta_gptq(delta, bits)
+        ops.convert_from_gptq(qw, qz, sc, bits, out=(full[0][d], full[1][d], full[2][d]))
+        sq, sz, ss = shard_gptq_tensors(qw, qz, sc, bits, "row", rank, world)
+        layer.set_delta(d, bits, sq, sz, ss, None, None)
+    ref = ops.apply_delta(x, full[0], full[2], full[1], idx, w).float()
+    layer.set_mapping(idx, None, None, None, [m])
+    y_tp = layer(x[:, lo:hi].contiguous())[0].float()
+    torch.cuda.synchronize()
+    rel = ((y_tp - ref).norm() / ref.norm()).item()
+    assert rel < 1e-2, rel
+    assert h.status() == 0
+
+    # --- bounded wait: rank 0 issues a call nobody joins ---
+    dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        lonely = torch.ones(4096, device=dev, dtype=torch.float16)
+        h.all_reduce(lonely)
+        torch.cuda.synchronize()            # returns after the kernel's one-second limit
+        assert h.status() == _lib.DZ_ERR_TIMEOUT, h.status()
+        z = torch.ones(8, device=dev) * 2   # the context is still usable
+        assert float(z.sum().item()) == 16.0
+    dist.barrier()
+    parallel_state.destroy_model_parallel()
+    dist.destroy_process_group()
+    print(f"ALLREDUCE_WORKER_OK rank {rank}", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -93,3 +93,32 @@ def test_tensor_parallel_collectives_gloo_world2():
             p.join(120)
             assert p.exitcode == 0
         assert dict(ret) == {0: True, 1: True}
+
+
+def test_shard_gptq_tensors_matches_slices_of_the_dense_delta():
+    """Unpacking a rank's GPTQ shard gives the matching slice of the unsharded dense delta,
+    for column (N) and row (K) parallel cuts and 2/4 bits."""
+    import numpy as np
+    from oracle import deltazip_oracle as orc
+    from deltazip_b200.models import shard_gptq_tensors
+    from deltazip_b200.parallel_state import shard_range
+    rng = np.random.default_rng(5)
+    n, k = 384, 320
+    for bits in (2, 4):
+        delta = (rng.standard_normal((n, k)) * 1e-2).astype(np.float32)
+        wq, scale, zero = orc.compress_delta(delta, bits)
+        packed = orc.pack(wq, scale, zero, bits)
+        qw, qz, sc = (torch.from_numpy(np.ascontiguousarray(t)) for t in packed[:3])
+        dense = orc.unpack(packed[0], packed[1], packed[2], bits)   # [N, K]
+        for world in (2, 3):
+            for rank in range(world):
+                cq, cz, cs = shard_gptq_tensors(qw, qz, sc, bits, "column", rank, world)
+                lo, hi = shard_range(n, 128, rank, world)
+                got = orc.unpack(cq.numpy(), cz.numpy(), cs.numpy(), bits)
+                assert got.shape == (hi - lo, k) and np.array_equal(got, dense[lo:hi])
+        for world in (2, 5):
+            for rank in range(world):
+                rq, rz, rs = shard_gptq_tensors(qw, qz, sc, bits, "row", rank, world)
+                lo, hi = shard_range(k, 64, rank, world)
+                got = orc.unpack(rq.numpy(), rz.numpy(), rs.numpy(), bits)
+                assert got.shape == (n, hi - lo) and np.array_equal(got, dense[:, lo:hi])
