@@ -82,7 +82,7 @@ constexpr int kPrefetchTiles = 8;               // W half-tiles prefetched to L2
 //   dcols = 128 : 3 classes, 6 buffers -> 256 + 192 + 24 = 472 columns
 
 struct Params {
-  int M, N, K, bits;
+  int M, N, K, bits, num_slots;
   int num_kunits, num_tiles, num_kblocks;
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
   int base_only, tokens_sorted;
@@ -422,7 +422,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ WinS s_win[kMaxWin];
   __shared__ int s_slot[kTokenBlock];   // slot of each column of the token block (-1: base only)
   __shared__ uint32_t s_tmem_base;
-  __shared__ int s_abort, s_last;
+  __shared__ int s_abort, s_last, s_npre;
 
   // INSTR only: per-CTA wall-clock marks of the last launch (8 x u64 per CTA) in the upper
   // part of the counter region
@@ -527,24 +527,75 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (INSTR && threadIdx.x == 0) tl[1] = globaltimer();
 
+  // The first x and W tiles are requested at once; the producer warp skips them later.
+  if (threadIdx.x == 0) {
+    int issued = 0;
+    const int npre = min(p.w_stages, p.x_stages);
+    for (int u = u_begin; u < u_end && issued < npre; ++u) {
+      const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
+      const int nhalf = min(2, (p.K - k0) / kBlockK);
+      for (int h = 0; h < nhalf && issued < npre; ++h, ++issued) {
+        const uint32_t xfull = smem_u32(&bar_x_full[issued]);
+        mbar_expect_tx(xfull, p.xb_bytes);
+        tma_load_2d(s_xring + issued * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
+        const uint32_t wfull = smem_u32(&bar_w_full[issued]);
+        mbar_expect_tx(wfull, kWTile);
+        tma_load_2d(s_wring + issued * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+      }
+    }
+    s_npre = issued;
+  }
+
   // ---- the batch: windows and per-column slots of this token block ----
+  // The table's array offsets follow from (M, num_slots), which the call states; the header
+  // must agree.  All reads below are independent of each other (one L2 round trip): the
+  // windows of token block 0 start at entry 0, and entries beyond the block's count are read
+  // (inside the table) but never used.
   int nwin = 0;
   bool bad = false;
   const int* perm = nullptr;
   const int* slot_of = nullptr;
-  const Window* gwin = nullptr;
   if (p.seg) {
     const SegHeader* hdr = reinterpret_cast<const SegHeader*>(p.seg);
-    bad = p.tokens_sorted && !hdr->sorted;
-    const SegLayout lay = seg_layout(hdr->capacity_M, hdr->num_slots);
+    const SegLayout lay = seg_layout(p.M, p.num_slots);
     perm = reinterpret_cast<const int*>(p.seg + lay.perm);
     slot_of = reinterpret_cast<const int*>(p.seg + lay.slot_of);
-    if (!p.base_only && !bad) {
-      const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
-      const int win_begin = bb[p.token_block];
-      nwin = min(bb[p.token_block + 1] - win_begin, kMaxWin);
-      gwin = reinterpret_cast<const Window*>(p.seg + lay.windows) + win_begin;
+    const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
+    const Window* wins = reinterpret_cast<const Window*>(p.seg + lay.windows);
+    const int hdr_m = hdr->capacity_M, hdr_slots = hdr->num_slots, hdr_sorted = hdr->sorted;
+    const int win_end = p.base_only ? 0 : bb[p.token_block + 1];
+    int win_begin = 0;
+    if (p.token_block == 0) {
+      const int cap = min(kMaxWin, seg_max_windows(p.M, p.num_slots));
+      if (!p.base_only && (int)threadIdx.x < cap) {
+        const Window w = wins[threadIdx.x];
+        WinS ws;
+        ws.slot = w.slot;
+        ws.col0 = w.col0 - p.row0;
+        ws.ncols = w.ncols;
+        ws.lohi = (w.lo - w.col0) | ((w.hi - w.col0) << 16);
+        s_win[threadIdx.x] = ws;
+      }
+    } else if (!p.base_only) {
+      win_begin = bb[p.token_block];
     }
+    bad = (hdr_m != p.M) || (hdr_slots != p.num_slots) || (p.tokens_sorted && !hdr_sorted);
+    if (!p.base_only && !bad) nwin = min(win_end - win_begin, kMaxWin);
+    if (p.token_block != 0) {
+      for (int i = threadIdx.x; i < nwin; i += kThreads) {
+        const Window w = wins[win_begin + i];
+        WinS ws;
+        ws.slot = w.slot;
+        ws.col0 = w.col0 - p.row0;
+        ws.ncols = w.ncols;
+        ws.lohi = (w.lo - w.col0) | ((w.hi - w.col0) << 16);
+        s_win[i] = ws;
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < kTokenBlock; i += kThreads) {
+    const int prow = p.row0 + i;
+    s_slot[i] = (slot_of && !p.base_only && prow < p.M) ? slot_of[prow] : -1;
   }
   if (threadIdx.x == 0) {
     // freed by the base issuer's commit and, when there are windows, by every thread of every
@@ -554,19 +605,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     mbar_init(smem_u32(bar_acc_full), 1 + (nwin > 0 ? C : 0));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (bad && blockIdx.x == 0) atomicCAS(p.status, 0, (int)DZ_ERR_INVALID_ARG);
-  }
-  for (int i = threadIdx.x; i < kTokenBlock; i += kThreads) {
-    const int prow = p.row0 + i;
-    s_slot[i] = (slot_of && !p.base_only && prow < p.M) ? slot_of[prow] : -1;
-  }
-  for (int i = threadIdx.x; i < nwin; i += kThreads) {
-    const Window w = gwin[i];
-    WinS ws;
-    ws.slot = w.slot;
-    ws.col0 = w.col0 - p.row0;
-    ws.ncols = w.ncols;
-    ws.lohi = (w.lo - w.col0) | ((w.hi - w.col0) << 16);
-    s_win[i] = ws;
   }
   // D_delta starts at zero (the delta MMAs always accumulate)
   if (warp >= kFirstWGWarp && nwin > 0) {
@@ -580,15 +618,23 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
 
   if (INSTR && threadIdx.x == 0) tl[2] = globaltimer();
+  const int npre = s_npre;
   const uint32_t a_col0 = 2 * p.dcols;          // TMEM column of expanded-A buffer 0
   const uint32_t e_col0 = a_col0 + nbuf * 32;   // TMEM column of metadata buffer 0
 
   if (bad) {
-    // rejected batch: nothing runs
+    // rejected batch: nothing runs, but the tiles requested in the prologue must land before
+    // this CTA's shared memory is released
+    if (threadIdx.x == 0)
+      for (int i = 0; i < npre; ++i) {
+        mbar_wait(smem_u32(&bar_x_full[i]), 0, abort_flag, nullptr);
+        mbar_wait(smem_u32(&bar_w_full[i]), 0, abort_flag, nullptr);
+      }
   } else if (warp == kWarpWX) {
     // ====================== TMA producer: W tiles and x half-tiles ======================
     if (lane == 0) {
       Ring rw(p.w_stages, 1), rx(p.x_stages, 1);
+      int cnt = 0;   // half-tiles so far; the first `npre` were requested in the prologue
       for (int u = u_begin; u < u_end;) {
         const int tile = u / KU, ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
@@ -597,15 +643,18 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const int k0 = ku * kUnitK;
           const int nhalf = min(2, (p.K - k0) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
-            mbar_wait(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status);
-            const uint32_t xfull = smem_u32(&bar_x_full[rx.idx]);
-            mbar_expect_tx(xfull, p.xb_bytes);
-            tma_load_2d(s_xring + rx.idx * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
+            if (cnt >= npre) {
+              mbar_wait(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status);
+              const uint32_t xfull = smem_u32(&bar_x_full[rx.idx]);
+              mbar_expect_tx(xfull, p.xb_bytes);
+              tma_load_2d(s_xring + rx.idx * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
+              mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
+              const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
+              mbar_expect_tx(wfull, kWTile);
+              tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+            }
+            ++cnt;
             rx.advance();
-            mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
-            const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
-            mbar_expect_tx(wfull, kWTile);
-            tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
             rw.advance();
           }
         }
@@ -1133,7 +1182,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   if (rc) return rc;
 
   Params p;
-  p.M = a.M; p.N = a.N; p.K = a.K; p.bits = a.bits;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.bits = a.bits; p.num_slots = a.num_slots;
   p.num_kblocks = a.K / kBlockK;
   p.num_kunits = (a.K + kUnitK - 1) / kUnitK;
   p.num_tiles = a.N / kTileN;
