@@ -25,7 +25,8 @@ static int check_sbmm_args(const dz_sbmm_args* a, bool base_only) {
   if (!a) return DZ_ERR_INVALID_ARG;
   if (a->M < 0) return DZ_ERR_INVALID_ARG;
   if (a->M == 0) return DZ_OK;  // nothing to do; pointers may be null
-  if (!a->x || !a->w_base || !a->y) return DZ_ERR_INVALID_ARG;
+  // w_base may be absent for dz_sbmm: only the delta products are then computed
+  if (!a->x || !a->y || (base_only && !a->w_base)) return DZ_ERR_INVALID_ARG;
   int rc = check_shape(a->N, a->K, base_only ? 4 : a->bits);
   if (rc) return rc;
   if (a->dtype != DZ_DTYPE_F16 && a->dtype != DZ_DTYPE_BF16) return DZ_ERR_INVALID_ARG;

@@ -85,7 +85,7 @@ struct Params {
   int M, N, K, bits, num_slots;
   int num_kunits, num_tiles, num_kblocks;
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
-  int base_only, tokens_sorted;
+  int base_only, delta_only, tokens_sorted;   // delta_only: no base product (w_base absent)
   int debug;
   int grid, total_units, epi_units;   // total_units counts virtual units
   int w_stages, x_stages, r_per_class, xb_bytes;
@@ -496,7 +496,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // pull the first W tiles of this CTA's range towards L2 (a prefetch consumes no data, so it
     // is safe whatever the predecessor writes)
     int issued = 0;
-    for (int u = u_begin; u < u_end && issued < kPrefetchTiles; ++u) {
+    for (int u = u_begin; u < u_end && issued < kPrefetchTiles && !p.delta_only; ++u) {
       const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
       const int nhalf = min(2, (p.K - k0) / kBlockK);
       for (int h = 0; h < nhalf; ++h, ++issued)
@@ -538,9 +538,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t xfull = smem_u32(&bar_x_full[issued]);
         mbar_expect_tx(xfull, p.xb_bytes);
         tma_load_2d(s_xring + issued * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
-        const uint32_t wfull = smem_u32(&bar_w_full[issued]);
-        mbar_expect_tx(wfull, kWTile);
-        tma_load_2d(s_wring + issued * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+        if (!p.delta_only) {
+          const uint32_t wfull = smem_u32(&bar_w_full[issued]);
+          mbar_expect_tx(wfull, kWTile);
+          tma_load_2d(s_wring + issued * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+        }
       }
     }
     s_npre = issued;
@@ -628,7 +630,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (threadIdx.x == 0)
       for (int i = 0; i < npre; ++i) {
         mbar_wait(smem_u32(&bar_x_full[i]), 0, abort_flag, nullptr);
-        mbar_wait(smem_u32(&bar_w_full[i]), 0, abort_flag, nullptr);
+        if (!p.delta_only) mbar_wait(smem_u32(&bar_w_full[i]), 0, abort_flag, nullptr);
       }
   } else if (warp == kWarpWX) {
     // ====================== TMA producer: W tiles and x half-tiles ======================
@@ -648,10 +650,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const uint32_t xfull = smem_u32(&bar_x_full[rx.idx]);
               mbar_expect_tx(xfull, p.xb_bytes);
               tma_load_2d(s_xring + rx.idx * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
-              mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
-              const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
-              mbar_expect_tx(wfull, kWTile);
-              tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+              if (!p.delta_only) {
+                mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
+                const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
+                mbar_expect_tx(wfull, kWTile);
+                tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+              }
             }
             ++cnt;
             rx.advance();
@@ -717,13 +721,15 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
             mbar_wait(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status);
-            mbar_wait(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status);
-            tc_fence_after();
-            if (INSTR && u == u_begin && ku == ku0 && h == 0) tl[3] = globaltimer();
-            umma_ss_x4(tmem_base, desc_lo(s_wring + rw.idx * kWTile),
-                       desc_lo(s_xring + rx.idx * p.xb_bytes), idesc_base, acc);
-            acc = 1;
-            umma_commit(smem_u32(&bar_w_empty[rw.idx]));
+            if (!p.delta_only) {
+              mbar_wait(smem_u32(&bar_w_full[rw.idx]), rw.par, abort_flag, p.status);
+              tc_fence_after();
+              if (INSTR && u == u_begin && ku == ku0 && h == 0) tl[3] = globaltimer();
+              umma_ss_x4(tmem_base, desc_lo(s_wring + rw.idx * kWTile),
+                         desc_lo(s_xring + rx.idx * p.xb_bytes), idesc_base, acc);
+              acc = 1;
+              umma_commit(smem_u32(&bar_w_empty[rw.idx]));
+            }
             umma_commit(smem_u32(&bar_x_empty[rx.idx]));
             rw.advance();
             rx.advance();
@@ -951,7 +957,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int hb = 0; hb < 2; ++hb) {
           const int col = c * 16 + hb * 8;
           uint32_t v[8], d[8];
-          tmem_ld8(lane_addr + col, v);
+          if (p.delta_only) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0;
+          } else {
+            tmem_ld8(lane_addr + col, v);
+          }
           if (nwin > 0) tmem_ld8(lane_addr + p.dcols + col, d);
           tmem_wait_ld();
           if (nwin > 0) {
@@ -1178,8 +1189,15 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
 
   CUtensorMap map_w, map_xc;
   const int dt = (a.dtype == DZ_DTYPE_BF16) ? 1 : 0;
-  int rc = make_map(&map_w, a.w_base, a.N, a.K, 128, dt);
-  if (rc) return rc;
+  int rc = DZ_OK;
+  if (a.w_base) {
+    rc = make_map(&map_w, a.w_base, a.N, a.K, 128, dt);
+    if (rc) return rc;
+  } else if (base_only) {
+    return DZ_ERR_INVALID_ARG;
+  } else {
+    memset(&map_w, 0, sizeof(map_w));   // never used: the kernel issues no W loads
+  }
 
   Params p;
   p.M = a.M; p.N = a.N; p.K = a.K; p.bits = a.bits; p.num_slots = a.num_slots;
@@ -1187,6 +1205,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.num_kunits = (a.K + kUnitK - 1) / kUnitK;
   p.num_tiles = a.N / kTileN;
   p.base_only = base_only ? 1 : 0;
+  p.delta_only = (!base_only && a.w_base == nullptr) ? 1 : 0;
   { const char* e = getenv("DZ_DEBUG"); p.debug = e ? atoi(e) : 0; }
   p.tokens_sorted = sorted ? 1 : 0;
   p.epi_units = kEpilogueUnits;

@@ -180,18 +180,23 @@ def _bits_from_shapes(qweight_stacked: torch.Tensor, k: int) -> int:
 
 
 def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
-         meta_stacked: torch.Tensor, segments: Segments, base_weight: torch.Tensor,
+         meta_stacked: torch.Tensor, segments: Segments, base_weight: Optional[torch.Tensor],
          out: Optional[torch.Tensor] = None, bits: Optional[int] = None,
          _entry: str = "dz_sbmm") -> torch.Tensor:
-    """y = x W^T + x dequant(delta_slot(i))^T with a prebuilt segment table."""
-    _need_cuda(x, qweight_stacked, scales_stacked, meta_stacked, base_weight)
+    """y = x W^T + x dequant(delta_slot(i))^T with a prebuilt segment table.  With
+    `base_weight=None` only the delta products are computed (rows of slot -1 get 0)."""
+    _need_cuda(x, qweight_stacked, scales_stacked, meta_stacked)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
     m, k = x2.shape
-    n = base_weight.shape[0]
-    if base_weight.shape[1] != k or not base_weight.is_contiguous():
-        raise ValueError("base_weight must be a contiguous [N, K] tensor matching x")
+    if base_weight is None:
+        n = scales_stacked.shape[-1]
+    else:
+        _need_cuda(base_weight)
+        n = base_weight.shape[0]
+        if base_weight.shape[1] != k or not base_weight.is_contiguous():
+            raise ValueError("base_weight must be a contiguous [N, K] tensor matching x")
     if segments.m != m:
         raise ValueError(f"segment table was built for {segments.m} tokens, x has {m}")
     if bits is None:
@@ -203,7 +208,7 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
     nbytes = lib().dz_sbmm_workspace_bytes(m, n, k, int(segments.sorted))
     ws = _workspace(x.device, nbytes)
     args = SbmmArgs(
-        x=x2.data_ptr(), w_base=base_weight.data_ptr(),
+        x=x2.data_ptr(), w_base=base_weight.data_ptr() if base_weight is not None else None,
         qweight=qweight_stacked.data_ptr(), meta=meta_stacked.data_ptr(),
         scales=scales_stacked.data_ptr(),
         qweight_stride=qweight_stacked.stride(0) * 4, meta_stride=meta_stacked.stride(0) * 2,
@@ -255,6 +260,76 @@ def apply_delta(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: 
         _segment_cache[key] = seg
     seg.build(indices)
     return sbmm(x, qweight_stacked, scales_stacked, meta_stacked, seg, base_weight)
+
+
+# ---------------------------------------------------------------------------
+# the "separate base output" form of the op: y += x dequant(delta)^T in place
+# ---------------------------------------------------------------------------
+
+def _segments_for(indices: torch.Tensor, num_slots: int, device) -> Segments:
+    m = indices.numel()
+    key = (device.index, _stream(), num_slots)
+    seg = _segment_cache.get(key)
+    if seg is None or seg.max_tokens < m:
+        seg = Segments(max(m, 256), num_slots, device)
+        _segment_cache[key] = seg
+    return seg.build(indices)
+
+
+def add_delta(y: torch.Tensor, x: torch.Tensor, qweight: torch.Tensor,
+              qzeros: Optional[torch.Tensor], scales: torch.Tensor,
+              g_idx: Optional[torch.Tensor], indices: torch.Tensor,
+              meta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In place y[i] += x[i] @ dequant(delta[indices[i]])^T, -1 = nothing added: the
+    reference's add_delta (serving/vllm/delta/deltazip.py:14-38) on slot-layout stacks
+    (`qweight`, `scales`, `meta` as `alloc_slots` makes them; the symmetric zero point and the
+    single quantisation group are implicit, so `qzeros` and `g_idx` are accepted and ignored).
+    The delta products come from the SBMM kernel without its base half; the addition to the
+    caller's base output is one elementwise pass over [M, N]."""
+    if meta is None:
+        raise ValueError("slot-layout stacks need their 2:4 metadata (meta)")
+    x2 = x.reshape(-1, x.shape[-1])
+    y2 = y.view(-1, y.shape[-1])
+    seg = _segments_for(indices.reshape(-1), qweight.shape[0], x.device)
+    y2 += sbmm(x2, qweight, scales, meta, seg, None)
+    return y
+
+
+def add_delta_slice(y: torch.Tensor, x: torch.Tensor, qweight: torch.Tensor,
+                    qzeros: Optional[torch.Tensor], scales: torch.Tensor,
+                    g_idx: Optional[torch.Tensor], indices: torch.Tensor, scale: float,
+                    y_offset: int, y_slice_size: int, *, buffer: Optional[torch.Tensor] = None,
+                    meta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """add_delta into the columns [y_offset, y_offset + y_slice_size) of y
+    (serving/vllm/delta/deltazip.py:41-78; `scale` and `buffer` are unused there too)."""
+    if meta is None:
+        raise ValueError("slot-layout stacks need their 2:4 metadata (meta)")
+    x2 = x.reshape(-1, x.shape[-1])
+    y2 = y.view(-1, y.shape[-1])
+    seg = _segments_for(indices.reshape(-1), qweight.shape[0], x.device)
+    part = sbmm(x2, qweight, scales, meta, seg, None)
+    if part.shape[-1] != y_slice_size:
+        raise ValueError(f"slice of {y_slice_size} columns, delta stack has {part.shape[-1]}")
+    y2[:, y_offset:y_offset + y_slice_size] += part
+    return y
+
+
+def apply_delta_packed_nslice(x: torch.Tensor, qweight_stacked, qzeros_stacked, scales_stacked,
+                              g_idx_stacked, indices: torch.Tensor, output: torch.Tensor,
+                              output_slices, meta_stacked=None) -> torch.Tensor:
+    """Merged layers (q/k/v, gate/up) whose sub-layers keep separate stacks: one add_delta_slice
+    per output slice (serving/vllm/delta/deltazip.py:108-153)."""
+    if meta_stacked is None:
+        raise ValueError("slot-layout stacks need their 2:4 metadata (meta_stacked)")
+    x2 = x.reshape(-1, x.shape[-1])
+    out2 = output.view(-1, output.shape[-1])
+    offset = 0
+    for i, width in enumerate(output_slices):
+        add_delta_slice(out2, x2, qweight_stacked[i], qzeros_stacked[i] if qzeros_stacked else None,
+                        scales_stacked[i], g_idx_stacked[i] if g_idx_stacked else None,
+                        indices, 1.0, offset, width, meta=meta_stacked[i])
+        offset += width
+    return output
 
 
 # ---------------------------------------------------------------------------

@@ -107,7 +107,11 @@ int dz_build_segments(const void* indices, int index_dtype, int M, int num_slots
  */
 typedef struct {
   const void* x;            /* [M, K] row-major, 16-byte aligned                 */
-  const void* w_base;       /* [N, K] row-major, 16-byte aligned                 */
+  const void* w_base;       /* [N, K] row-major, 16-byte aligned; NULL for dz_sbmm:
+                               y = x dequant(delta)^T only (rows of slot -1 get 0),
+                               the product the reference's GPTQ-layout ops add to a
+                               separately computed base output
+                               (serving/vllm/delta/deltazip.py:14-153)             */
   const void* qweight;      /* slot 0 of the qweight stack                       */
   const void* meta;         /* slot 0 of the meta stack                          */
   const void* scales;       /* slot 0 of the scales stack                        */

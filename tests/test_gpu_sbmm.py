@@ -174,3 +174,51 @@ def test_bf16_activations_and_base(bits):
     assert ops.read_status() == 0
     yb = ops.base_gemm(xb, wb)
     assert O.rel_l2(yb.float().cpu().numpy(), (xb.float() @ wb.float().t()).cpu().numpy()) <= 5e-3
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_add_delta_in_place_matches_the_separate_base_output_path(bits):
+    """The GPTQ-layout form of the op (base output first, delta added in place,
+    serving/vllm/delta/deltazip.py:14-38): y = fp16(x W^T) + delta products."""
+    from deltazip_b200 import ops
+    layer = DeviceLayer(384, 512, 5, bits, seed=21)
+    x, idx = O.make_tokens(40, 512, 5, seed=9)
+    xd, idxd = dev(x), dev(idx)
+    # delta products alone (no base weight): rows of slot -1 are exactly zero
+    seg = ops.Segments(len(idx), layer.num_slots, "cuda").build(idxd)
+    only = ops.sbmm(xd, layer.qweight, layer.scales, layer.meta, seg, None)
+    dense = layer.dense()
+    want = np.zeros((len(idx), 384), np.float32)
+    for i, s in enumerate(idx):
+        if s >= 0:
+            want[i] = x[i].astype(np.float32) @ dense[s].astype(np.float32).T
+    torch.cuda.synchronize()
+    got = only.float().cpu().numpy()
+    assert O.rel_l2(got, want) <= 2e-3
+    assert not got[np.asarray(idx) < 0].any()
+    # in place on top of a base output
+    y = ops.base_gemm(xd, layer.w)
+    base = y.clone()
+    ret = ops.add_delta(y, xd, layer.qweight, None, layer.scales, None, idxd, meta=layer.meta)
+    assert ret.data_ptr() == y.data_ptr()
+    torch.cuda.synchronize()
+    assert torch.equal(y, base + only)
+    check(layer, x, idx, y.cpu().numpy())
+
+
+def test_apply_delta_packed_nslice_merged_layer():
+    """Three sub-layers with their own stacks written into slices of one output."""
+    from deltazip_b200 import ops
+    widths = (256, 128, 128)
+    layers_ = [DeviceLayer(w, 256, 3, 4, seed=30 + i) for i, w in enumerate(widths)]
+    x, idx = O.make_tokens(20, 256, 3, seed=4)
+    xd, idxd = dev(x), dev(idx)
+    out = torch.cat([ops.base_gemm(xd, l.w) for l in layers_], dim=1)
+    ops.apply_delta_packed_nslice(xd, [l.qweight for l in layers_], None, [l.scales for l in layers_],
+                                  None, idxd, out, widths, meta_stacked=[l.meta for l in layers_])
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    off = 0
+    for l, w in zip(layers_, widths):
+        check(l, x, idx, got[:, off:off + w])
+        off += w
