@@ -263,16 +263,6 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* v) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
@@ -308,6 +298,24 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b,
 }
 __device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// shared-memory accesses by 32-bit shared address (volatile: they keep their order relative to
+// the barrier waits, which are volatile too)
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w));
 }
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -439,7 +447,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // ---- shared memory carve-up (1024-byte aligned regions) ----
   const uint32_t dyn0 = smem_u32(smem_dyn);
   const uint32_t sbase = (dyn0 + 1023u) & ~1023u;
-  uint8_t* const sgen = smem_dyn + (sbase - dyn0);
   const uint32_t s_wring = sbase;
   const uint32_t off_x = p.w_stages * kWTile;
   const uint32_t off_win = off_x + p.x_stages * p.xb_bytes;
@@ -447,9 +454,6 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t s_xring = sbase + off_x;
   const uint32_t s_winbuf = sbase + off_win;
   const uint32_t s_rring = sbase + off_r;
-  uint8_t* const g_xring = sgen + off_x;
-  uint8_t* const g_winbuf = sgen + off_win;
-  uint8_t* const g_rring = sgen + off_r;
 
   uint64_t* bar_w_full = s_bars;
   uint64_t* bar_w_empty = bar_w_full + kMaxW;
@@ -796,13 +800,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int k0 = ku * kUnitK;
         const int nhalf = min(2, (p.K - k0) / kBlockK);
         // the unit's x half-tiles
-        const uint8_t* xsrc0 = nullptr;
-        const uint8_t* xsrc1 = nullptr;
+        uint32_t xsrc0 = 0, xsrc1 = 0;
         int xslot0 = 0, xslot1 = 0;
         for (int h = 0; h < nhalf; ++h) {
           mbar_wait(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status);
-          if (h == 0) { xsrc0 = g_xring + rx.idx * p.xb_bytes; xslot0 = rx.idx; }
-          else { xsrc1 = g_xring + rx.idx * p.xb_bytes; xslot1 = rx.idx; }
+          if (h == 0) { xsrc0 = s_xring + rx.idx * p.xb_bytes; xslot0 = rx.idx; }
+          else { xsrc1 = s_xring + rx.idx * p.xb_bytes; xslot1 = rx.idx; }
           rx.advance();
         }
         for (int j = 0; j < cnt_t; ++j, ++n) {
@@ -813,25 +816,25 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (++rs == p.r_per_class) { rs = 0; rpar ^= 1; }
           mbar_wait(smem_u32(&bar_a_free[buf]), ((n >> 1) & 1) ^ 1, abort_flag, p.status);
           tc_fence_after();
-          const uint8_t* raw = g_rring + rslot * kRStage;
-          uint8_t* const my_win = g_winbuf + buf * kWinBytes;
+          const uint32_t raw = s_rring + rslot * kRStage;
+          const uint32_t my_win = s_winbuf + buf * kWinBytes;
           uint32_t mw[4] = {0, 0, 0, 0};
           for (int h = 0; h < nhalf; ++h) {
             uint32_t o[16];
             if (BITS == 4) {
-              const uint4 cw = *reinterpret_cast<const uint4*>(raw + h * 2048 + r * 16);
+              const uint4 cw = lds128(raw + h * 2048 + r * 16);
               const uint32_t wv[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
               for (int wi = 0; wi < 4; ++wi) expand_word4<DT>(wv[wi], o + wi * 4);
             } else {
-              const uint2 cw = *reinterpret_cast<const uint2*>(raw + h * 1024 + r * 8);
+              const uint2 cw = lds64(raw + h * 1024 + r * 8);
               const uint32_t wv[2] = {cw.x, cw.y};
 #pragma unroll
               for (int wi = 0; wi < 2; ++wi) expand_word2<DT>(wv[wi], o + wi * 8);
             }
             // compressed A of this half: 32 fp16 = 16 columns of the row's lane
             tmem_st16(lane_addr + a_col0 + buf * 32 + h * 16, o);
-            const uint2 m2 = *reinterpret_cast<const uint2*>(raw + kRawBytes + h * 1024 + r * 8);
+            const uint2 m2 = lds64(raw + kRawBytes + h * 1024 + r * 8);
             mw[h * 2] = m2.x;
             mw[h * 2 + 1] = m2.y;
           }
@@ -843,16 +846,15 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
             const int per_half = ws.ncols * 8;           // 16-byte chunks
             const int total = nhalf * per_half;
-            const uint8_t* x0 = xsrc0 + (size_t)ws.col0 * 128;
-            const uint8_t* x1 = xsrc1 + (size_t)ws.col0 * 128 - (size_t)per_half * 16;
+            const uint32_t x0 = xsrc0 + ws.col0 * 128;
+            const uint32_t x1 = xsrc1 + ws.col0 * 128 - per_half * 16;
 #pragma unroll 2
             for (int idx = wg_tid; idx < total; idx += 128) {
               const bool h = idx >= per_half;
               const int row = (idx - (h ? per_half : 0)) >> 3;
               uint4 v = make_uint4(0, 0, 0, 0);
-              if (row >= lo && row < hi)
-                v = *reinterpret_cast<const uint4*>((h ? x1 : x0) + (size_t)idx * 16);
-              *reinterpret_cast<uint4*>(my_win + (size_t)idx * 16) = v;
+              if (row >= lo && row < hi) v = lds128((h ? x1 : x0) + idx * 16);
+              sts128(my_win + idx * 16, v);
             }
           }
           fence_proxy_async();
