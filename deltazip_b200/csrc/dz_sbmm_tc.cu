@@ -819,7 +819,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint32_t raw = s_rring + rslot * kRStage;
           const uint32_t my_win = s_winbuf + buf * kWinBytes;
           uint32_t mw[4] = {0, 0, 0, 0};
-          for (int h = 0; h < nhalf; ++h) {
+          auto expand_half = [&](const int h) {
             uint32_t o[16];
             if (BITS == 4) {
               const uint4 cw = lds128(raw + h * 2048 + r * 16);
@@ -837,24 +837,30 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint2 m2 = lds64(raw + kRawBytes + h * 1024 + r * 8);
             mw[h * 2] = m2.x;
             mw[h * 2 + 1] = m2.y;
-          }
+          };
+          expand_half(0);
+          if (nhalf == 2) expand_half(1);
           tmem_st4(lane_addr + e_col0 + buf * 4, mw[0], mw[1], mw[2], mw[3]);
           // the packed stage has been consumed
           mbar_arrive(smem_u32(&bar_r_empty[rslot]));
           // the slot's token window: rows of the resident x half-tiles, other slots' rows zeroed
+          // (16-byte chunk c of a half = row c >> 3; both halves' chunks are requested together)
           {
             const int lo = ws.lohi & 0xFFFF, hi = ws.lohi >> 16;
-            const int per_half = ws.ncols * 8;           // 16-byte chunks
-            const int total = nhalf * per_half;
             const uint32_t x0 = xsrc0 + ws.col0 * 128;
-            const uint32_t x1 = xsrc1 + ws.col0 * 128 - per_half * 16;
-#pragma unroll 2
-            for (int idx = wg_tid; idx < total; idx += 128) {
-              const bool h = idx >= per_half;
-              const int row = (idx - (h ? per_half : 0)) >> 3;
-              uint4 v = make_uint4(0, 0, 0, 0);
-              if (row >= lo && row < hi) v = lds128((h ? x1 : x0) + idx * 16);
-              sts128(my_win + idx * 16, v);
+            const uint32_t x1 = xsrc1 + ws.col0 * 128;
+            const uint32_t half_bytes = ws.ncols * 128;
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            for (int c = wg_tid; c < ws.ncols * 8; c += 128) {
+              const int row = c >> 3;
+              const bool in = row >= lo && row < hi;
+              uint4 v0 = zero4, v1 = zero4;
+              if (in) {
+                v0 = lds128(x0 + c * 16);
+                if (nhalf == 2) v1 = lds128(x1 + c * 16);
+              }
+              sts128(my_win + c * 16, v0);
+              if (nhalf == 2) sts128(my_win + half_bytes + c * 16, v1);
             }
           }
           fence_proxy_async();
