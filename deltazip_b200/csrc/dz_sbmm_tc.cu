@@ -308,10 +308,18 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
                : "r"(a));
   return v;
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
   uint2 v;
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
   return v;
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v));
 }
 __device__ __forceinline__ void sts128(uint32_t a, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z),
@@ -426,11 +434,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xc,
                const Params p) {
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t s_bars[2 * kMaxW + 2 * kMaxX + 2 * kMaxR + 2 * kMaxBuf + 2];
+  __shared__ __align__(8) uint64_t s_bars[2 * kMaxW + 2 * kMaxX + 2 * kMaxR + 2 * kMaxBuf + 2 + kNumWG];
   __shared__ WinS s_win[kMaxWin];
   __shared__ int s_slot[kTokenBlock];   // slot of each column of the token block (-1: base only)
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_last, s_npre;
+  __shared__ uint32_t s_fixpar[kNumWG];
 
   // INSTR only: per-CTA wall-clock marks of the last launch (8 x u64 per CTA) in the upper
   // part of the counter region
@@ -450,7 +459,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t s_wring = sbase;
   const uint32_t off_x = p.w_stages * kWTile;
   const uint32_t off_win = off_x + p.x_stages * p.xb_bytes;
-  const uint32_t off_r = off_win + nbuf * kWinBytes;
+  const uint32_t off_r = off_win + 2 * kNumWG * kWinBytes;   // every warpgroup owns two
   const uint32_t s_xring = sbase + off_x;
   const uint32_t s_winbuf = sbase + off_win;
   const uint32_t s_rring = sbase + off_r;
@@ -465,6 +474,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint64_t* bar_a_free = bar_a_ready + kMaxBuf;
   uint64_t* bar_acc_full = bar_a_free + kMaxBuf;
   uint64_t* bar_acc_empty = bar_acc_full + 1;
+  uint64_t* bar_fix = bar_acc_empty + 1;   // per warpgroup: parked partials landed in its scratch
 
   // ---- this CTA's unit range ----
   const int cta = blockIdx.x;
@@ -492,6 +502,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(smem_u32(&bar_a_free[i]), 1);
     }
     mbar_init(smem_u32(bar_acc_empty), 128 * kNumWG);
+    for (int i = 0; i < kNumWG; ++i) {
+      mbar_init(smem_u32(&bar_fix[i]), 1);
+      s_fixpar[i] = 0;
+    }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -883,9 +897,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // leaves with a single fire-and-forget release increment.
       const bool full_tile = (ku0 == 0 && ku1 == KU);
       int c_first = 0, nfrag = 1, ticket = 0;
+      uint32_t slot_first = 0;   // parking slot (0/1) of the tile's first fragment
       if (!full_tile) {
         c_first = split_owner(tile, 0, p.grid, KU, p.epi_units, U);
         nfrag = split_owner(tile, KU - 1, p.grid, KU, p.epi_units, U) - c_first + 1;
+        slot_first = (split_begin(c_first, p.grid, KU, p.epi_units, U) / KU == tile) ? 0u : 1u;
         if (ep_tid == 0) ticket = atomicAdd(&p.counters[2 * tile], 1);
       }
       // D_delta holds sums of (code - zero) * x; the per-channel scale of each
@@ -944,8 +960,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         named_bar_sync(1, 128 * kNumWG);
         last = s_last != 0;
       }
-      float* my_partial = p.partials +
-                          ((size_t)cta * 2 + (cta_first_fragment ? 0 : 1)) * ((size_t)p.cols * 128);
+      // this fragment's parking slot, as a float index into the partials
+      const uint32_t my_park = (uint32_t)(cta * 2 + (cta_first_fragment ? 0 : 1)) * (uint32_t)(p.cols * 128);
+      // phase of the warpgroup's fix-up barrier (kept in shared memory between fragments)
+      uint32_t fixpar = last ? s_fixpar[wg] : 0;
       for (int c = wg; c < p.cols / 16; c += kNumWG) {
         if (nwin > 0 && c != wg) {   // second chunk of a wide token block: its scales are fetched here
 #pragma unroll
@@ -982,40 +1000,62 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
           }
           if (last) {
-            // sum over the tile's fragments in CTA order, this fragment's accumulators taking
-            // their own place in that order; 8 columns x 2 fragments per pass keep 16
-            // independent L2 loads in flight
+            // Sum over the tile's fragments in CTA order, this fragment's accumulators taking
+            // their own place in that order.  Everything is summed out of shared memory: the
+            // thread's own 8 values go to slot 3 of the scratch, the other fragments' parked
+            // columns arrive three fragments at a time by bulk copies (one L2 round trip for
+            // 3 x 8 columns).  The scratch is the warpgroup's own two window buffers, idle
+            // until its next expansion.
             const int my_f = cta - c_first;
-            float sum[8];
+            const uint32_t scr0 = s_winbuf + (wg < C ? wg : 2 * C + 2 * (wg - C)) * kWinBytes + r * 4;
+            const uint32_t scr1 = scr0 + (wg < C ? C : 1) * kWinBytes;
+            const uint32_t fixbar = smem_u32(&bar_fix[wg]);
+            named_bar_sync(2 + wg, 128);   // nobody still reads the scratch (previous columns)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-            for (int f0 = 0; f0 < nfrag; f0 += 2) {
-              float part[2][8];
+            for (int i = 0; i < 8; ++i) sts32(scr1 + 4096 + i * 512, v[i]);
 #pragma unroll
-              for (int ff = 0; ff < 2; ++ff) {
-                const int f = f0 + ff;
-                if (f < nfrag && f != my_f) {
-                  const int cc = c_first + f;
-                  const int cu0 = split_begin(cc, p.grid, KU, p.epi_units, U);
-                  const int slot = cc * 2 + ((cu0 / KU) == tile ? 0 : 1);
-                  const float* src =
-                      p.partials + (size_t)slot * ((size_t)p.cols * 128) + (size_t)col * 128 + r;
+            for (int i = 0; i < 8; ++i) v[i] = 0;   // from here on v is the running sum
+            for (int j = 0; j < nfrag - 1; j += 3) {
+              const int cnt = min(3, nfrag - 1 - j);
+              if (j > 0) named_bar_sync(2 + wg, 128);
+              if (wg_tid == 0) {
+                fence_proxy_async();
+                mbar_expect_tx(fixbar, cnt * 4096);
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) part[ff][i] = __ldcg(src + i * 128);
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 8; ++i)
-                    part[ff][i] = (f == my_f) ? __uint_as_float(v[i]) : 0.f;
+                for (int ff = 0; ff < 3; ++ff) {
+                  if (ff >= cnt) break;
+                  const int o = j + ff;   // o-th other fragment = fragment o, or o + 1 past this one
+                  const int f = o + (o >= my_f ? 1 : 0);
+                  // only the tile's first fragment can be its CTA's second parking slot
+                  const uint32_t slot = (uint32_t)(c_first + f) * 2 + (f == 0 ? slot_first : 0);
+                  const uint32_t off = (slot * (uint32_t)p.cols + (uint32_t)col) * 512u;
+                  bulk_load((ff < 2 ? scr0 : scr1) - r * 4 + (ff & 1) * 4096,
+                            reinterpret_cast<const uint8_t*>(p.partials) + off, 4096, fixbar);
                 }
               }
+              mbar_wait(fixbar, fixpar, abort_flag, p.status);
+              fixpar ^= 1;
 #pragma unroll
-              for (int ff = 0; ff < 2; ++ff)
+              for (int ff = 0; ff < 3; ++ff) {
+                if (ff >= cnt) break;
+                if (j + ff == my_f) {   // this fragment comes right before its successor
+#pragma unroll
+                  for (int i = 0; i < 8; ++i)
+                    v[i] = __float_as_uint(__uint_as_float(v[i]) +
+                                           __uint_as_float(lds32(scr1 + 4096 + i * 512)));
+                }
+                const uint32_t src = (ff < 2 ? scr0 : scr1) + (ff & 1) * 4096;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  if (f0 + ff < nfrag) sum[i] += part[ff][i];
+                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(lds32(src + i * 512)));
+              }
             }
+            if (my_f == nfrag - 1) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __float_as_uint(sum[i]);
+              for (int i = 0; i < 8; ++i)
+                v[i] = __float_as_uint(__uint_as_float(v[i]) +
+                                       __uint_as_float(lds32(scr1 + 4096 + i * 512)));
+            }
           }
           if (full_tile || last) {
 #pragma unroll
@@ -1029,7 +1069,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              __stcg(my_partial + (size_t)(col + i) * 128 + r, __uint_as_float(v[i]));
+              __stcg(p.partials + (my_park + (uint32_t)((col + i) * 128 + r)), __uint_as_float(v[i]));
           }
         }
         if (nwin > 0) tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
@@ -1037,6 +1077,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(bar_acc_empty));
+      // (every thread read s_fixpar before the first barrier of its fix-up rounds)
+      if (last && wg_tid == 0) s_fixpar[wg] = fixpar;
 
       if (!full_tile && !last) {
         // release pattern: every thread's partial stores happen before the barrier; one
@@ -1244,7 +1286,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     p.nclass = p.cols <= 64 ? 4 : 3;
     p.x_stages = p.cols <= 64 ? 4 : 3;
     p.w_stages = 3;
-    const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + 2 * p.nclass * kWinBytes;
+    const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + 2 * kNumWG * kWinBytes;
     p.r_per_class = min(4, (kSmemBudget - fixed) / (p.nclass * kRStage));
     if (p.r_per_class < 2 || p.nclass * p.r_per_class > kMaxR) return DZ_ERR_UNSUPPORTED;
     rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols, dt);
