@@ -73,7 +73,7 @@ constexpr int kTmemCols = 512;
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
 constexpr int kMaxCtas = 160;
 constexpr int kSmemBudget = 216 * 1024;
-constexpr int kEpilogueUnits = 1;               // cost of a tile's epilogue in k-units (work split)
+constexpr int kEpilogueUnits = 2;               // cost of a tile's epilogue in k-units (work split)
 constexpr int kPrefetchTiles = 8;               // W half-tiles prefetched to L2 in the prologue
 
 // TMEM columns: D_base [0, dcols), D_delta [dcols, 2 dcols), then 32 columns of
