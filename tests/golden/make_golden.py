@@ -76,7 +76,9 @@ def reference_case(quant, qlinear, n, k, bits, m, seed, zero_row=False):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of a deltazip checkout>")
+    ref = sys.argv[1]
     quant = _load(os.path.join(ref, "deltazip/core/quant.py"), "ref_quant")
     qlinear = _load(os.path.join(ref, "deltazip/nn_modules/qlinear.py"), "ref_qlinear")
     torch.set_num_threads(8)
