@@ -29,7 +29,7 @@
 // the issuers interleave.
 //
 // Work split.  (tile, k-unit of 128) pairs are divided over one CTA per SM
-// ("stream-K", with a tile's epilogue counted as one more unit): a CTA walks a
+// ("stream-K", with a tile's epilogue counted as two more units): a CTA walks a
 // contiguous unit range, which may cover the tail of one tile, whole tiles and
 // the head of another.  The fragments of a split tile settle it through two
 // per-tile counters: each claims a ticket; all but the holder of the last
