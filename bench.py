@@ -1,20 +1,23 @@
 #!/usr/bin/env python
-"""Benchmark of the SBMM hot path on the Llama-2-7B projection shapes.
+"""Benchmarks of the SBMM hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4|5]
 
-Workload (the SBMM microbenchmark configuration): the four delta linears of a
-Llama-2-7B decoder layer -- qkv 12288x4096, o 4096x4096, gate_up 22016x4096,
-down 4096x11008 -- for all 32 layers, fp16 base ~ N(0, 0.02), 8 resident deltas
-(4-bit, 2:4, symmetric, per-channel scale, delta ~ N(0, 1e-3)), a decode batch of
-64 tokens whose slot ids are uniform over the 8 deltas (sorted, as the
-scheduler delivers them).  One step = one decode pass through all 128 SBMM
-calls; the weights of a step (32 GB) are far larger than L2, so every step
-streams them from HBM.  Data are seeded and synthetic.
+--config 2 (default, the headline): the SBMM microbenchmark configuration.  The four delta
+linears of a Llama-2-7B decoder layer -- qkv 12288x4096, o 4096x4096, gate_up 22016x4096,
+down 4096x11008 -- for all 32 layers, fp16 base ~ N(0, 0.02), 8 resident deltas (4-bit, 2:4,
+symmetric, per-channel scale, delta ~ N(0, 1e-3)), a decode batch of 64 tokens whose slot ids
+are uniform over the 8 deltas (sorted, as the scheduler delivers them).  One step = one decode
+pass through all 128 SBMM calls; the weights of a step (32 GB) are far larger than L2, so every
+step streams them from HBM.  Data are seeded and synthetic.
 
-N > 1: tensor parallel over N ranks (column-parallel qkv / gate_up, row-parallel
-o / down followed by an NCCL all-reduce), shards cut at whole 128-row tiles and
-64-column blocks; the total work is fixed ("strong" scaling).
+--config 3 / 4: full-model decode through deltazip_b200/engine.py: Llama-2-7B with 32 resident
+2-bit deltas and 128 sequences; Llama-2-13B with 64 2-bit deltas, 256 sequences and a Zipf(1.5)
+request-to-delta map, tensor parallel.
+
+N > 1: tensor parallel over N ranks (column-parallel qkv / gate_up, row-parallel o / down
+followed by the library's peer-memory all-reduce), shards cut at whole 128-wide units; the total
+work is fixed ("strong" scaling).
 
 One JSON line is printed by rank 0.
 """
@@ -39,19 +42,17 @@ METRIC = "sbmm_decode_tokens_per_s"
 UNIT = "tok/s"
 
 
-def projections(tp: int, rank: int):
-    """(name, N, K, row_parallel) per rank; shards are whole 128-row tiles / 64-col blocks."""
-    def split(total, unit):
-        units = total // unit
-        lo = units * rank // tp
-        hi = units * (rank + 1) // tp
-        return (hi - lo) * unit
-    qkv = 3 * split(HIDDEN, 128)
-    gate_up = 2 * split(INTER, 128)
-    return [("qkv_proj", qkv, HIDDEN, False),
-            ("o_proj", HIDDEN, split(HIDDEN, 64), True),
-            ("gate_up_proj", gate_up, HIDDEN, False),
-            ("down_proj", HIDDEN, split(INTER, 64), True)]
+def projections(tp: int, rank: int, hidden: int = HIDDEN, inter: int = INTER):
+    """(name, N, K, row_parallel) per rank.  Column- and row-parallel layers are cut at the same
+    128-wide units, so that a producer's shard is its consumer's K range for every rank count."""
+    def split(total):
+        units = total // 128
+        return (units * (rank + 1) // tp - units * rank // tp) * 128
+    h, i = split(hidden), split(inter)
+    return [("qkv_proj", 3 * h, hidden, False),
+            ("o_proj", hidden, h, True),
+            ("gate_up_proj", 2 * i, hidden, False),
+            ("down_proj", hidden, i, True)]
 
 
 def algorithmic_bytes(m, n, k, active, bits):
@@ -111,6 +112,11 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def dist_env():
+    return (int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
 def build_model(tp, rank, device, seed=0, num_layers=LAYERS):
     """Per layer and projection: base weight, slot stacks.  Deltas are generated and
     compressed once per projection shape and replicated (device copies) per layer."""
@@ -136,25 +142,84 @@ def build_model(tp, rank, device, seed=0, num_layers=LAYERS):
     return projs, layers
 
 
+def dense_reference(x, e, idx):
+    """float32 y = x W^T + x dequant(delta_slot)^T from the unpacked slots (the unpack is
+    pinned bit-exact to the reference's QuantLinear.unpack by the parity tests)."""
+    import torch
+    from deltazip_b200 import ops
+    y = x.float() @ e["w"].float().t()
+    for s in torch.unique(idx).tolist():
+        if s < 0:
+            continue
+        rows = (idx == s).nonzero().flatten()
+        dense = ops.unpack(e["q"][s], e["m"][s], e["s"][s], e["n"], e["k"], BITS)
+        y[rows] += x[rows].float() @ dense.float().t()
+    return y
+
+
+def allreduce_selfcheck(car, rank, world, device):
+    """Values of the peer-memory all-reduce against the rank-order float32 sum of the gathered
+    inputs, bit for bit: several sizes and dtypes, the produce-in-staging path, and a run of
+    back-to-back calls (the two staging buffers alternate).  Returns "ok" or what differed."""
+    import torch
+    import torch.distributed as dist
+
+    def expected(x):
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        acc = torch.zeros(x.shape, dtype=torch.float32, device=device)
+        for p in parts:                      # rank order, fp32, one rounding: the kernel's rule
+            acc += p.float()
+        return acc.to(x.dtype)
+
+    # every rank runs every call whatever it finds (the calls are collective); the first
+    # difference is kept and the verdict is agreed on at the end
+    bad = None
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    for dtype in (torch.float16, torch.bfloat16, torch.float32):
+        for numel in (8, 4096, 64 * 4096, 256 * 5120, 1 << 20):
+            x = torch.randn(numel, generator=g, device=device).to(dtype)
+            want = expected(x)
+            got = car.all_reduce(x)
+            if bad is None and not torch.equal(got, want):
+                bad = f"mismatch dtype={dtype} numel={numel}"
+    for it in range(100):                    # produced directly in the staging buffer
+        st = car.staging_like((TOKENS, HIDDEN), torch.float16)
+        st.copy_(torch.randn((TOKENS, HIDDEN), generator=g, device=device).half())
+        want = expected(st.clone())
+        got = car.all_reduce(st)
+        if bad is None and not torch.equal(got, want):
+            bad = f"staging path mismatch at call {it}"
+    torch.cuda.synchronize()
+    st = car.status()
+    if bad is None and st != 0:
+        bad = f"status {st}"
+    flag = torch.tensor([0 if bad is None else 1], device=device)
+    dist.all_reduce(flag)
+    if flag.item() == 0:
+        return "ok"
+    return bad if bad is not None else "mismatch on another rank"
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
     from deltazip_b200 import _lib, ops
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world, rank, local_rank = dist_env()
     if args.gpus > 1 and world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     car = None
+    ar_check = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
         if args.allreduce == "custom":
             # the library's peer-memory all-reduce for the row-parallel outputs
             from deltazip_b200 import custom_all_reduce
             car = custom_all_reduce.init_custom_ar(rank, world)
+            ar_check = allreduce_selfcheck(car, rank, world, device)
     tp = world
     L = _lib.lib()
 
@@ -162,6 +227,7 @@ def run_ours(args):
     g = torch.Generator(device="cpu").manual_seed(1234)
     idx_host = torch.sort(torch.randint(0, NUM_DELTAS, (TOKENS,), generator=g))[0].to(torch.int64)
     active = len(set(idx_host.tolist()))
+    # one activation per distinct K of this rank (a row-parallel layer sees its own K range)
     x_host = {k: torch.randn((TOKENS, k), generator=g).half().pin_memory()
               for k in sorted({p[2] for p in projs})}
     idx_pinned = idx_host.pin_memory()
@@ -195,35 +261,61 @@ def run_ours(args):
 
     stage_ptr, stage_len = ctypes.c_void_p(), ctypes.c_size_t()
 
-    def step_device():
-        n_launch = 0
-        for a, rowp, y in calls:
-            reduce = rowp and tp > 1
-            if reduce and car is not None:
-                # the SBMM writes its partial output straight into the staging buffer of the
-                # all-reduce that follows (buffers alternate from call to call)
-                L.dz_allreduce_staging(car._ctx, ctypes.byref(stage_ptr), ctypes.byref(stage_len))
-                a.y = stage_ptr.value
-            rc = L.dz_sbmm(ctypes.byref(a), stream)
+    def launch(a, rowp, y, collectives=True):
+        """One projection: the SBMM and, for a row-parallel layer under tensor parallelism, the
+        all-reduce of its partial output.  Returns the number of this library's launches."""
+        reduce = rowp and tp > 1 and collectives
+        if reduce and car is not None:
+            # the SBMM writes its partial output straight into the staging buffer of the
+            # all-reduce that follows (buffers alternate from call to call)
+            L.dz_allreduce_staging(car._ctx, ctypes.byref(stage_ptr), ctypes.byref(stage_len))
+            a.y = stage_ptr.value
+        else:
+            a.y = y.data_ptr()
+        rc = L.dz_sbmm(ctypes.byref(a), stream)
+        if rc:
+            _lib.check(rc, "dz_sbmm")
+        if not reduce:
+            return 1
+        if car is not None:
+            rc = L.dz_allreduce_run(car._ctx, stage_ptr, y.data_ptr(), y.numel(),
+                                    _lib.DZ_DTYPE_F16, stream)
             if rc:
-                _lib.check(rc, "dz_sbmm")
-            n_launch += 1
-            if reduce:
-                if car is not None:
-                    rc = L.dz_allreduce_run(car._ctx, stage_ptr, y.data_ptr(), y.numel(),
-                                            _lib.DZ_DTYPE_F16, stream)
-                    if rc:
-                        _lib.check(rc, "dz_allreduce_run")
-                    n_launch += 1
-                else:
-                    dist.all_reduce(y)
-        return n_launch
+                _lib.check(rc, "dz_allreduce_run")
+            return 2
+        dist.all_reduce(y)
+        return 1
+
+    def step_device(collectives=True):
+        return sum(launch(a, rowp, y, collectives) for a, rowp, y in calls)
 
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
+
+    # ---- parity of the launches that get timed (outside the timed region) ----
+    # layer 0, all four shapes, every output: SBMM against dequantise-then-matmul in float32;
+    # under tensor parallelism the all-reduced output against the all-reduce (NCCL, float32)
+    # of the per-rank dense references.
+    parity = {"max_rel_l2": 0.0, "shapes": {}}
+    for (a, rowp, y), (name, n, k, _) in zip(calls[:len(projs)], projs):
+        launch(a, rowp, y)
+        ref = dense_reference(x_dev[k], layers[0][name], idx_dev)
+        if rowp and tp > 1:
+            dist.all_reduce(ref)
+        torch.cuda.synchronize()
+        rel = ((y.float() - ref).norm() / ref.norm()).item()
+        parity["shapes"][f"{name} {n}x{k}"] = rel
+        parity["max_rel_l2"] = max(parity["max_rel_l2"], rel)
+    parity["tolerance"] = 1e-2
+    parity["ok"] = bool(parity["max_rel_l2"] <= 1e-2)
+    if world > 1:
+        flag = torch.tensor([parity["max_rel_l2"]], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        parity["max_rel_l2"] = flag.item()
+        parity["ok"] = bool(parity["max_rel_l2"] <= 1e-2)
 
     # ---- device-resident timing (value) ----
     for _ in range(args.warmup):
@@ -242,20 +334,27 @@ def run_ours(args):
         launches += step_device()
     ev1.record()
     barrier()
-    t_wall1 = time.time()
     ms_total = ev0.elapsed_time(ev1)
     status = ops_read_status(L, ws, stream)
 
-    # ---- kernel-only time for the roofline: same launches, no collectives ----
-    kev0, kev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    kev0.record()
-    for a, _, y in calls:
-        a.y = y.data_ptr()
-        L.dz_sbmm(ctypes.byref(a), stream)
-    kev1.record()
-    torch.cuda.synchronize()
-    kernel_ms = kev0.elapsed_time(kev1)
+    # ---- time of the SBMM launches alone, for the roofline ----
+    # One GPU: the timed region above holds nothing but the SBMM launches, so the average launch
+    # time is that region's.  Several GPUs: the same number of warmed steps without the
+    # collectives, timed the same way.
+    if world == 1:
+        kernel_ms = ms_total
+        kernel_src = "the timed steps"
+    else:
+        step_device(collectives=False)
+        barrier()
+        kev0, kev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        kev0.record()
+        for _ in range(args.steps):
+            step_device(collectives=False)
+        kev1.record()
+        torch.cuda.synchronize()
+        kernel_ms = kev0.elapsed_time(kev1)
+        kernel_src = "a separate pass of the same steps without the all-reduce"
 
     # ---- end to end through the public API: host buffers in, host result out ----
     def step_e2e():
@@ -298,8 +397,9 @@ def run_ours(args):
     if rank == 0:
         ms_per_step = ms_total / args.steps
         peaks = measured_peaks()
-        achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
         n_calls = len(calls)
+        kernel_ms_per_step = kernel_ms / args.steps
+        achieved = step_bytes / (kernel_ms_per_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": TOKENS / (ms_per_step * 1e-3), "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -313,7 +413,7 @@ def run_ours(args):
                 "tokens": TOKENS, "deltas": NUM_DELTAS, "active_deltas": active, "bits": BITS,
                 "layers": args.layers, "sbmm_calls_per_step": n_calls,
                 "parallelism": f"tp{world}",
-                "allreduce": ("peer-memory one-shot (dz_allreduce_run)" if car is not None
+                "allreduce": ("peer-memory (dz_allreduce_run)" if car is not None
                               else ("nccl" if world > 1 else "none")),
                 "l2": "inputs larger than L2: each step streams %.1f GB of distinct weights"
                       % (step_bytes * 1e-9),
@@ -324,16 +424,20 @@ def run_ours(args):
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches,
             "roofline": {
-                "bound": "hbm", "kernel": "sbmm_tc_kernel<4>",
+                "bound": "hbm", "kernel": "sbmm_tc_kernel<4,0>",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": step_bytes / n_calls,
-                "avg_launch_us": kernel_ms * 1e3 / n_calls,
+                "avg_launch_us": kernel_ms_per_step * 1e3 / n_calls,
+                "timed_over": kernel_src,
                 "traffic": ncu_traffic_per_launch(step_bytes / n_calls),
             },
+            "parity_check": parity,
             "clocks": clocks,
             "kernel_status": status,
         }
+        if ar_check is not None:
+            line["allreduce_check"] = ar_check
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
         print(json.dumps(line), flush=True)
@@ -345,6 +449,10 @@ def run_ours(args):
             from deltazip_b200 import custom_all_reduce
             custom_all_reduce.destroy_custom_ar()
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
+    if ar_check not in (None, "ok"):
+        raise SystemExit(f"all-reduce check failed: {ar_check}")
 
 
 def ops_read_status(L, ws, stream):
@@ -375,85 +483,463 @@ def ncu_traffic_per_launch(alg_bytes_per_launch):
 
 
 # ---------------------------------------------------------------------------
-# CPU arm: the oracle's torch-CPU port of the reference path, on the host cores
+# CPU arm: the reference's own PyTorch path on the host cores
 # ---------------------------------------------------------------------------
 
-def cpu_sample(threads):
-    """One o_proj-shaped call (4096x4096, 8 deltas, 64 tokens) of the reference's CPU path."""
-    import torch
-    from oracle import torch_port as T
-    torch.set_num_threads(threads)
-    g = torch.Generator().manual_seed(7)
-    n = k = HIDDEN
-    w = (torch.randn((n, k), generator=g) * 0.02).half()
-    x = torch.randn((TOKENS, k), generator=g).half()
-    idx = torch.sort(torch.randint(0, NUM_DELTAS, (TOKENS,), generator=g))[0]
-    # one packed delta reused for every slot: the CPU time does not depend on the values
-    per = 32 // BITS
-    qweight = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // per, n), generator=g, dtype=torch.int64).to(torch.int32)
-    qzeros = torch.full((1, n // per), 0x77777777, dtype=torch.int32)
-    scales = (torch.rand((1, n), generator=g) * 1e-3 + 1e-4).half()
-    deltas = [(qweight, qzeros, scales, BITS)] * NUM_DELTAS
-    return lambda: T.apply_delta(x, w, deltas, idx, dequant_every_call=True)
+class CpuLayerSample:
+    """One decoder layer of the benchmark (its four SBMM calls) on the host: fp16 base weights,
+    deltas 2:4-pruned and quantised by the quantiser (so the codes are genuinely 2:4), packed in
+    the reference's GPTQ layout.  One compressed delta per shape is shared by the 8 slots: the
+    CPU path's time does not depend on the values, and generating 8 x 4 full-size deltas on the
+    host would take longer than timing them.
 
+    With oracle/_ref present (the reference's own quant.py / qlinear.py staged by
+    oracle/make_ref.py) the calls run QuantLinear.forward itself: kind "reference".  Otherwise
+    they run the restatement in oracle/torch_port.py: kind "port"."""
 
-def layer_scale_factor():
-    """How many 4096x4096 calls one full decode step is worth, by weight count."""
-    per_layer = sum(n * k for _, n, k, _ in projections(1, 0))
-    return LAYERS * per_layer / float(HIDDEN * HIDDEN)
+    def __init__(self, threads: int):
+        import torch
+        from deltazip_b200 import synth                      # data preparation only
+        from oracle import reference_path as R
+        from oracle import torch_port as T
+        torch.set_num_threads(threads)
+        self.kind = "reference" if R.available() else "port"
+        g = torch.Generator().manual_seed(7)
+        self.idx = torch.sort(torch.randint(0, NUM_DELTAS, (TOKENS,), generator=g))[0]
+        self.calls = []
+        gen_dev = "cuda" if torch.cuda.is_available() else "cpu"
+        for name, n, k, _ in projections(1, 0):
+            w = (torch.randn((n, k), generator=g) * 0.02).half()
+            x = torch.randn((TOKENS, k), generator=g).half()
+            delta = (torch.randn((n, k), generator=g) * 1e-3).to(gen_dev)
+            qw, qz, sc = (t.cpu() for t in synth.compress_delta_gptq(delta, BITS))
+            del delta
+            if self.kind == "reference":
+                layer = R.quant_linear(qw, qz, sc, BITS)
+                layers = [layer] * NUM_DELTAS
+                self.calls.append((name, n, k, lambda pre=None, x=x, w=w, layers=layers:
+                                   R.apply_delta(x, w, layers, self.idx, pre), layer))
+            else:
+                deltas = [(qw, qz, sc, BITS)] * NUM_DELTAS
+                self.calls.append((name, n, k, lambda pre=None, x=x, w=w, deltas=deltas:
+                                   T.apply_delta(x, w, deltas, self.idx, dequant_every_call=pre is None,
+                                                 cache=pre), None))
+        self._pre = None
+
+    def run_layer(self):
+        """The reference's behaviour: dequantise every call."""
+        for _, _, _, fn, _ in self.calls:
+            fn()
+
+    def time_each(self, reps: int):
+        """Median seconds per call for each shape, dequantising every call."""
+        out = {}
+        for name, n, k, fn, _ in self.calls:
+            ts = []
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                fn()
+                ts.append(time.perf_counter() - t0)
+            out[f"{name} {n}x{k}"] = sorted(ts)[len(ts) // 2]
+        return out
+
+    def time_pre_unpacked(self, reps: int):
+        """Same calls with the dense deltas unpacked beforehand (pure matmul cost)."""
+        import torch
+        from oracle import reference_path as R
+        from oracle import torch_port as T
+        out = {}
+        for name, n, k, fn, layer in self.calls:
+            if self.kind == "reference":
+                pre = [R.unpack_dense_t(layer)] * NUM_DELTAS
+            else:
+                pre = {}
+                fn(pre)                                     # fills the cache
+            ts = []
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                fn(pre)
+                ts.append(time.perf_counter() - t0)
+            out[f"{name} {n}x{k}"] = sorted(ts)[len(ts) // 2]
+            del pre
+        return out
 
 
 def cpu_baseline(budget_s=20.0):
-    import torch
     threads = os.cpu_count() or 1
-    fn = cpu_sample(threads)
-    fn()
+    sample = CpuLayerSample(threads)
+    sample.run_layer()                                      # warm-up
     t0 = time.perf_counter()
-    reps = 0
-    while True:
-        fn()
-        reps += 1
-        if time.perf_counter() - t0 > budget_s or reps >= 50:
-            break
-    per_call = (time.perf_counter() - t0) / reps
-    step_s = per_call * layer_scale_factor()
-    return {"value": TOKENS / step_s, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": "oracle/torch_port.apply_delta (dequantise every call, as the reference's "
-                      "PyTorch path does) on one 4096x4096 layer, 8 deltas, 64 tokens, %d reps, "
-                      "%.3f s per call; scaled by weight count (x%.1f) to the 128-call step"
-                      % (reps, per_call, layer_scale_factor())}
+    per_call = sample.time_each(reps=1)
+    layer_s = sum(per_call.values())
+    reps = int(max(1, min(5, budget_s / max(layer_s, 1e-3) - 1)))
+    if reps > 1:
+        per_call = sample.time_each(reps=reps)
+        layer_s = sum(per_call.values())
+    pre = sample.time_pre_unpacked(reps=max(1, min(3, reps)))
+    step_s = layer_s * LAYERS
+    return {"value": TOKENS / step_s, "unit": UNIT, "cores": threads, "kind": sample.kind,
+            "sample": "one decoder layer = one call of each of the four shapes (8 deltas, 64 tokens, "
+                      "quantiser-made 2:4 codes) through %s, dequantising on every call as the "
+                      "reference does; median of %d; x32 layers for the step"
+                      % ("the reference's QuantLinear.forward + F.linear (oracle/_ref)"
+                         if sample.kind == "reference" else "oracle/torch_port.apply_delta", reps),
+            "seconds_per_call": per_call,
+            "pre_unpacked": {"value": TOKENS / (sum(pre.values()) * LAYERS), "unit": UNIT,
+                             "seconds_per_call": pre},
+            "wall_s": time.perf_counter() - t0}
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
+    world, rank, _ = dist_env()
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    fn = cpu_sample(threads)
-    for _ in range(min(args.warmup, 2)):
-        fn()
-    steps = max(1, min(args.steps, 10))
+    sample = CpuLayerSample(threads)
+    warm = max(1, min(args.warmup, 2))
+    for _ in range(warm):
+        sample.run_layer()
+    steps = max(1, min(args.steps, 20))
     t0 = time.perf_counter()
     for _ in range(steps):
-        fn()
-    per_call = (time.perf_counter() - t0) / steps
-    step_s = per_call * layer_scale_factor()
+        sample.run_layer()
+    layer_s = (time.perf_counter() - t0) / steps
+    step_s = layer_s * LAYERS
     value = TOKENS / step_s
-    sample = ("each step = one 4096x4096 SBMM (8 deltas, 64 tokens) through the oracle's torch-CPU "
-              "port of the reference path, scaled by weight count (x%.1f) to the full 128-call "
-              "decode step; %d timed steps" % (layer_scale_factor(), steps))
+    text = ("each timed step = one decoder layer (one call of each of the four shapes, 8 deltas, 64 "
+            "tokens, quantiser-made 2:4 codes, dequantised on every call) = 1/32 of the benchmark's "
+            "decode step; value = 64 tokens / (32 x the mean step); %d timed steps; code: %s"
+            % (steps, "the reference's QuantLinear.forward + F.linear (oracle/_ref)"
+               if sample.kind == "reference" else "oracle/torch_port.apply_delta"))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": min(args.warmup, 2),
+        "n_gpus": world, "steps": steps, "warmup": warm,
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "configs[1]: SBMM over Llama-2-7B projection shapes x 32 layers, "
-                               "8 deltas 4-bit 2:4, 64-token decode batch (CPU arm: bounded sample)",
+        "config": {"workload": "configs[1]: SBMM over Llama-2-7B projection shapes (qkv 12288x4096, "
+                               "o 4096x4096, gate_up 22016x4096, down 4096x11008) x 32 layers, "
+                               "8 deltas 4-bit 2:4 sym per-channel, 64-token decode batch, slot ids "
+                               "uniform over 8 (sorted)",
+                   "sampled": "one of the 32 identical layers per timed step",
+                   "tokens": TOKENS, "deltas": NUM_DELTAS, "bits": BITS, "layers": LAYERS,
                    "parallelism": "cpu"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": sample.kind,
+                         "sample": text},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# Full-model decode configurations (3: 7B / 32 deltas, 4: 13B / 64 deltas Zipf, tensor parallel)
+# ---------------------------------------------------------------------------
+
+DECODE_CONFIGS = {
+    3: dict(model="llama-2-7b", deltas=32, bits=2, seqs=128, prompt=512, decode=128, zipf=None,
+            text="configs[2]: Llama-2-7B architecture (32 layers, hidden 4096, 32 heads, inter 11008, "
+                 "vocab 32000), random-init fp16 base, 32 resident 2-bit 2:4 deltas, 128 concurrent "
+                 "sequences, prompt 512, request-to-delta uniform, paged KV cache"),
+    4: dict(model="llama-2-13b", deltas=64, bits=2, seqs=256, prompt=256, decode=256, zipf=1.5,
+            text="configs[3]: Llama-2-13B architecture (40 layers, hidden 5120, 40 heads, inter 13824), "
+                 "random-init fp16 base, 64 deltas 2-bit 2:4, 256 sequences, request-to-delta Zipf "
+                 "alpha=1.5, prompt 256, tensor parallel"),
+}
+
+
+def request_deltas(num_seqs, num_deltas, zipf, seed=0):
+    """Delta id (1-based) of every sequence: uniform, or Zipf(alpha) over the delta ranks."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    if zipf is None:
+        return (torch.randint(0, num_deltas, (num_seqs,), generator=g) + 1).tolist()
+    p = 1.0 / torch.arange(1, num_deltas + 1, dtype=torch.float64) ** zipf
+    return (torch.multinomial(p / p.sum(), num_seqs, replacement=True, generator=g) + 1).tolist()
+
+
+def fill_resident_deltas(engine, resident, bits, seed=0):
+    """Writes seeded synthetic deltas (N(0, 1e-3), 2:4-pruned, quantised, packed and converted on
+    the device) straight into the GPU slots: distinct data per slot and projection shape for the
+    first layer, copied to the other layers (every byte the kernel streams is still distinct
+    memory; only the generation time is saved)."""
+    import torch
+    from deltazip_b200 import ops, synth
+    mgr = engine.manager
+    first = {}
+    for name, module in mgr.modules.items():
+        leaf = name.rsplit(".", 1)[1]
+        if leaf not in first:
+            n, k = module.weight.shape
+            gen = torch.Generator(device=engine.device).manual_seed(seed + len(first))
+            for slot in range(len(resident)):
+                delta = torch.randn((n, k), generator=gen, device=engine.device) * 1e-3
+                qw, qz, sc = synth.compress_delta_gptq(delta, bits)
+                del delta
+                ops.convert_from_gptq(qw, qz, sc, bits, check_status=(slot == 0),
+                                      out=(module.qweight_stacked[slot], module.meta_stacked[slot],
+                                           module.scales_stacked[slot]))
+            first[leaf] = module
+        else:
+            src = first[leaf]
+            module.qweight_stacked.copy_(src.qweight_stacked)
+            module.meta_stacked.copy_(src.meta_stacked)
+            module.scales_stacked.copy_(src.scales_stacked)
+    for slot, delta_id in enumerate(resident):
+        mgr.adopt_resident(delta_id, slot)
+
+
+def run_decode(args):
+    import torch
+    import torch.distributed as dist
+    from deltazip_b200 import _lib, ops, parallel_state
+    from deltazip_b200.config import DeltaConfig
+    from deltazip_b200.engine import DecodeEngine, Sequence
+    from deltazip_b200.llama import LLAMA2_7B, LLAMA2_13B, LlamaConfig
+
+    spec = DECODE_CONFIGS[args.config]
+    world, rank, local_rank = dist_env()
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        parallel_state.initialize_model_parallel(world, disable_custom_all_reduce=(args.allreduce == "nccl"))
+    base = LLAMA2_7B if spec["model"] == "llama-2-7b" else LLAMA2_13B
+    layers = args.layers or base.num_hidden_layers
+    cfg = LlamaConfig(base.hidden_size, base.intermediate_size, layers, base.num_attention_heads,
+                      base.num_key_value_heads, base.vocab_size)
+    bits, seqs_total, prompt = spec["bits"], spec["seqs"], spec["prompt"]
+    steps, warmup = args.steps, args.warmup
+    max_new = warmup + 2 * steps + 3 + 8                    # timed steps, end-to-end steps, margin
+
+    # ---- which deltas the batch needs, and how many of them fit ----
+    seq_delta = request_deltas(seqs_total, spec["deltas"], spec["zipf"])
+    demand = {}
+    for d in seq_delta:
+        demand[d] = demand.get(d, 0) + 1
+    needed = sorted(demand, key=lambda d: (-demand[d], d))
+    projs = projections(world, rank, cfg.hidden_size, cfg.intermediate_size)
+    slot_bytes = sum(n * k * (bits / 16 + 1 / 8) + 2 * n for _, n, k, _ in projs) * layers
+    base_bytes = sum(2 * n * k for _, n, k, _ in projs) * layers + 2 * 2 * cfg.vocab_size * cfg.hidden_size
+    kv_heads_local = max(1, cfg.kv_heads // world)
+    block = 16
+    blocks_per_seq = (prompt + max_new + block - 1) // block
+    kv_bytes = seqs_total * blocks_per_seq * block * kv_heads_local * 128 * 2 * 2 * layers
+    free, _total = torch.cuda.mem_get_info()
+    fit = int((free * 0.90 - base_bytes - kv_bytes) // slot_bytes)
+    if world > 1:
+        t = torch.tensor([fit], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        fit = int(t.item())
+    slots = max(1, min(len(needed), fit))
+    resident = needed[:slots]
+    admitted = [i for i, d in enumerate(seq_delta) if d in set(resident)]
+
+    engine = DecodeEngine(cfg, DeltaConfig(max_deltas=slots, max_bitwidth=bits, max_cpu_deltas=slots),
+                          max_seqs=seqs_total, kv_blocks=len(admitted) * blocks_per_seq, block_size=block,
+                          device=device)
+    fill_resident_deltas(engine, resident, bits)
+    # prefill is replaced by a synthetic cache of the prompt length: random keys and values
+    for li in range(layers):
+        engine.cache.k[li].normal_(0.0, 0.5)
+        engine.cache.v[li].normal_(0.0, 0.5)
+    g = torch.Generator().manual_seed(1)
+    first_tokens = torch.randint(0, cfg.vocab_size, (seqs_total,), generator=g).tolist()
+    for i in admitted:
+        s = Sequence(seq_id=i, delta_id=seq_delta[i], length=prompt, max_new=max_new)
+        s.blocks = engine.cache.allocate(blocks_per_seq)
+        engine.running.append(s)
+    engine._rebuild({i: first_tokens[i] for i in admitted})
+    b = len(engine.running)
+    active = len({s.delta_id for s in engine.running})
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident timing ----
+    for _ in range(warmup):
+        engine.decode_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_wall0 = time.time()
+    ev0.record()
+    for _ in range(steps):
+        engine.decode_step()
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    status = ops.read_status(device)
+
+    # ---- end to end: each step's inputs come from pinned host memory, its tokens go back ----
+    tok_host = engine.tokens.cpu().pin_memory()
+    pos_host = engine.positions.cpu().pin_memory()
+    out_host = torch.empty_like(tok_host).pin_memory()
+
+    def step_e2e():
+        engine.tokens = tok_host.to(device, non_blocking=True)
+        engine.positions = pos_host.to(device, non_blocking=True)
+        out = engine.decode_step()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        tok_host.copy_(out_host)
+        pos_host.add_(1)
+
+    step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop(t_wall0, time.time()) if rank == 0 else None
+
+    # ---- the SBMM launches of a step alone, for the roofline ----
+    mgr = engine.manager
+    xs = {k: torch.randn((b, k), device=device).half() for k in sorted({p[2] for p in projs})}
+    mods = [(m, xs[m.weight.shape[1]]) for _, m in sorted(mgr.modules.items())]
+
+    def sbmm_only():
+        for m, x in mods:
+            m.apply_weights(x)
+    sbmm_only()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(steps):
+        sbmm_only()
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / steps
+    step_bytes = sum(algorithmic_bytes(b, n, k, active, bits) for _, n, k, _ in projs) * layers
+
+    times = torch.tensor([ms_total, e2e_ms, kernel_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, kernel_ms = times.tolist()
+
+    if rank == 0:
+        ms_per_step = ms_total / steps
+        peaks = measured_peaks()
+        achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
+        n_calls = len(mods)
+        launches_per_step = n_calls + layers * (4 + (2 if world > 1 else 0)) + 2
+        line = {
+            "metric": "decode_tokens_per_s", "value": b / (ms_per_step * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {
+                "workload": spec["text"] + "; measured: decode steps of the whole batch (one token per "
+                            "sequence per step); prefill replaced by a synthetic KV cache of the prompt "
+                            "length (random keys/values)",
+                "layers": layers, "sequences_requested": seqs_total, "sequences_running": b,
+                "deltas": spec["deltas"], "deltas_needed_by_the_batch": len(needed),
+                "gpu_slots": slots, "active_deltas": active, "bits": bits, "context": prompt,
+                "parallelism": f"tp{world}",
+                "admission": ("all sequences run" if b == seqs_total else
+                              "GPU memory holds %d of the %d deltas the batch needs: sequences of the "
+                              "other deltas wait (delta-aware admission)" % (slots, len(needed))),
+                "l2": "inputs larger than L2: each step streams %.1f GB of weights per rank"
+                      % (step_bytes * 1e-9),
+            },
+            "e2e": {"value": b / (e2e_ms / steps * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(b * 16), "d2h_bytes_per_step": int(b * 8),
+                    "ms_per_step": e2e_ms / steps},
+            "gpu_launches": launches_per_step * steps,
+            "roofline": {
+                "bound": "hbm", "kernel": "sbmm_tc_kernel<%d,0>" % bits,
+                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": step_bytes / n_calls,
+                "avg_launch_us": kernel_ms * 1e3 / n_calls,
+                "timed_over": "a separate pass of the step's %d SBMM launches alone" % n_calls,
+                "sbmm_share_of_step": kernel_ms / ms_per_step,
+                "traffic": ncu_traffic_per_launch(step_bytes / n_calls),
+            },
+            "clocks": clocks, "kernel_status": status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_decode(cfg, b, active, bits, layers)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        from deltazip_b200 import custom_all_reduce
+        h = custom_all_reduce.get_handle()
+        if h is not None and h.status():
+            raise SystemExit("peer-memory all-reduce reported a status")
+        parallel_state.destroy_model_parallel()
+        dist.destroy_process_group()
+
+
+def cpu_sample_decode(cfg, tokens, active, bits, threads):
+    """One o_proj-shaped call ([hidden, hidden]) with the batch's tokens and active deltas through
+    the reference's CPU path (dequantise every delta on every call)."""
+    import torch
+    from deltazip_b200 import synth
+    from oracle import reference_path as R
+    from oracle import torch_port as T
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(3)
+    h = cfg.hidden_size
+    w = (torch.randn((h, h), generator=g) * 0.02).half()
+    x = torch.randn((tokens, h), generator=g).half()
+    idx = torch.sort(torch.arange(tokens) % active)[0]
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    qw, qz, sc = (t.cpu() for t in synth.compress_delta_gptq((torch.randn((h, h), generator=g) * 1e-3).to(dev), bits))
+    if R.available():
+        layer = R.quant_linear(qw, qz, sc, bits)
+        return "reference", lambda: R.apply_delta(x, w, [layer] * active, idx)
+    return "port", lambda: T.apply_delta(x, w, [(qw, qz, sc, bits)] * active, idx)
+
+
+def cpu_baseline_decode(cfg, tokens, active, bits, layers):
+    threads = os.cpu_count() or 1
+    kind, fn = cpu_sample_decode(cfg, tokens, active, bits, threads)
+    t0 = time.perf_counter()
+    fn()
+    per_call = time.perf_counter() - t0
+    reps = int(max(1, min(3, 15.0 / max(per_call, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    per_call = (time.perf_counter() - t0) / reps
+    weights = sum(n * k for _, n, k, _ in projections(1, 0, cfg.hidden_size, cfg.intermediate_size))
+    scale = layers * weights / float(cfg.hidden_size ** 2)
+    return {"value": tokens / (per_call * scale), "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": "extrapolated: one %dx%d SBMM call with the batch's %d tokens and %d active %d-bit "
+                      "deltas through the reference's CPU path (dequantise every call), %.2f s per call, "
+                      "scaled by weight count (x%.0f) to the linear layers of a decode step; attention and "
+                      "the other steps are not included" % (cfg.hidden_size, cfg.hidden_size, tokens, active,
+                                                            bits, per_call, scale)}
+
+
+def run_decode_reference(args):
+    from deltazip_b200.llama import LLAMA2_7B, LLAMA2_13B
+    world, rank, _ = dist_env()
+    if rank != 0:
+        return
+    spec = DECODE_CONFIGS[args.config]
+    cfg = LLAMA2_7B if spec["model"] == "llama-2-7b" else LLAMA2_13B
+    seq_delta = request_deltas(spec["seqs"], spec["deltas"], spec["zipf"])
+    active = len(set(seq_delta))
+    base = cpu_baseline_decode(cfg, spec["seqs"], active, spec["bits"], cfg.num_hidden_layers)
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": base["value"], "unit": UNIT,
+            "n_gpus": world, "steps": 1, "warmup": 1, "ms_per_step": spec["seqs"] / base["value"] * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": {"workload": spec["text"], "parallelism": "cpu"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
@@ -463,14 +949,29 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=LAYERS,
-                    help="decoder layers to instantiate (32 = the benchmark; fewer only for profiling captures)")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="2: SBMM microbenchmark (headline); 3/4/5: full-model decode configurations")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="decoder layers to instantiate (default: the model's; fewer only for "
+                         "profiling captures and smoke runs)")
     ap.add_argument("--allreduce", default="custom", choices=["custom", "nccl"],
                     help="N>1: all-reduce after the row-parallel layers (library peer-memory kernel or NCCL)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")
+    ap.add_argument("--duration", type=float, default=None,
+                    help="config 5: seconds of simulated arrivals (default 300)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    if args.config in DECODE_CONFIGS:
+        if args.impl == "reference":
+            run_decode_reference(args)
+        else:
+            run_decode(args)
+        return
+    if args.config == 5:
+        raise SystemExit("config 5 is not built in this version")
+    if args.layers is None:
+        args.layers = LAYERS
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libdeltazip_b200.so")
@@ -30,6 +30,7 @@ DZ_DTYPE_BF16 = 1
 DZ_DTYPE_F32 = 2
 DZ_INDEX_I32 = 0
 DZ_INDEX_I64 = 1
+DZ_SBMM_ACCUMULATE = 1
 
 
 class SbmmArgs(Structure):
@@ -41,8 +42,9 @@ class SbmmArgs(Structure):
         ("segments", c_void_p), ("y", c_void_p),
         ("M", c_int32), ("N", c_int32), ("K", c_int32),
         ("num_slots", c_int32), ("bits", c_int32), ("dtype", c_int32),
-        ("tokens_sorted", c_int32), ("reserved", c_int32),
+        ("tokens_sorted", c_int32), ("flags", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("y_stride", c_int64),
     ]
 
 
@@ -74,8 +76,17 @@ _SIGNATURES = {
     "dz_base_gemm": (c_int, [POINTER(SbmmArgs), c_void_p]),
     "dz_sbmm_static": (c_int, [POINTER(SbmmArgs), c_void_p]),
     "dz_sbmm_static_max_tokens": (c_int, []),
+    "dz_sbmm_static_status": (c_int, [c_void_p, POINTER(c_int)]),
     "dz_delta_embedding": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "dz_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
+    "dz_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "dz_rotary_and_cache": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                    c_int, c_int, c_float, c_int, c_void_p]),
+    "dz_paged_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "dz_paged_attention_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                          c_void_p, c_size_t, c_int, c_void_p]),
     "dz_slot_upload": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "dz_slot_reset": (c_int, [c_void_p, c_size_t, c_void_p]),
     "dz_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),

@@ -31,13 +31,13 @@ class CompressionConfig:
 
     def __post_init__(self):
         if not 0 <= self.sparsity <= 1:
-            raise ValueError("sparsity must be [0, 1]")
+            raise ValueError(f"sparsity {self.sparsity} lies outside [0, 1]")
         if self.bits not in (2, 3, 4, 8, 16):
-            raise ValueError("only support quantize to [2, 3, 4, 8, 16] bits.")
+            raise ValueError(f"{self.bits}-bit codes are not a supported width (2, 3, 4, 8, 16)")
         if self.group_size != -1 and self.group_size <= 0:
-            raise ValueError("unless equal to -1, group_size must greater then 0.")
+            raise ValueError("group_size is -1 (one group per row) or a positive count")
         if not 0 < self.damp_percent < 1:
-            raise ValueError("damp_percent must between 0 and 1.")
+            raise ValueError(f"damp_percent {self.damp_percent} lies outside (0, 1)")
         self.pack_factor = Fraction(32, self.bits)
 
     def to_dict(self):
@@ -76,7 +76,7 @@ class DeltaConfig:
         if self.max_cpu_deltas is None:
             self.max_cpu_deltas = self.max_deltas
         elif self.max_cpu_deltas < self.max_deltas:
-            raise ValueError("max_cpu_deltas must be greater than max_deltas")
+            raise ValueError("the pinned-host cache (max_cpu_deltas) cannot be smaller than the GPU slots (max_deltas)")
         if self.max_bitwidth not in (2, 4):
             raise ValueError("max_bitwidth must be 2 or 4")
         self.pack_factor = Fraction(32, self.max_bitwidth)

@@ -157,14 +157,11 @@ allreduce_oneshot_kernel(const ArParams p) {
     const int peer = threadIdx.x;
     unsigned* remote =
         reinterpret_cast<unsigned*>(p.peers[peer] + kFlagsOff) + p.rank * kMaxBlocks + b;
-    if (p.copy_in) {
-      // this block's copy must be visible to the peer before the flag
-      __threadfence_system();
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
-    } else {
-      // the slice was written by an earlier kernel, which has completed
-      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
-    }
+    // this block's copy (or, when the producer wrote the staging buffer directly, the earlier
+    // kernel's stores, ordered before this point by the dependency wait) must be visible to the
+    // peer before the flag: a system-scope release in both cases
+    if (p.copy_in) __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
     const unsigned* local =
         reinterpret_cast<const unsigned*>(mine + kFlagsOff) + peer * kMaxBlocks + b;
     unsigned long long t0 = 0;

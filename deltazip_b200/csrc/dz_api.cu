@@ -21,7 +21,7 @@ static int check_shape(int N, int K, int bits) {
   return DZ_OK;
 }
 
-static int check_sbmm_args(const dz_sbmm_args* a, bool base_only) {
+int check_sbmm_args(const dz_sbmm_args* a, bool base_only, bool check_workspace) {
   if (!a) return DZ_ERR_INVALID_ARG;
   if (a->M < 0) return DZ_ERR_INVALID_ARG;
   if (a->M == 0) return DZ_OK;  // nothing to do; pointers may be null
@@ -38,7 +38,12 @@ static int check_sbmm_args(const dz_sbmm_args* a, bool base_only) {
         (a->meta_stride & 15) || (a->scales_stride & 1))
       return DZ_ERR_ALIGNMENT;
   }
-  if (a->workspace_bytes < sbmm_workspace_bytes(a->M, a->N, a->K, base_only ? 1 : a->tokens_sorted)) return DZ_ERR_WORKSPACE;
+  if (a->flags & ~(int32_t)DZ_SBMM_ACCUMULATE) return DZ_ERR_INVALID_ARG;
+  if (a->y_stride != 0 && (a->y_stride < a->N || (a->y_stride & 7))) return DZ_ERR_INVALID_ARG;
+  if (!check_workspace) return DZ_OK;
+  if (a->workspace_bytes <
+      sbmm_workspace_bytes(a->M, a->N, a->K, base_only ? 1 : a->tokens_sorted))
+    return DZ_ERR_WORKSPACE;
   if (a->workspace_bytes && (!a->workspace || !aligned16(a->workspace))) return DZ_ERR_ALIGNMENT;
   return DZ_OK;
 }
@@ -123,22 +128,24 @@ size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted) {
 }
 
 int dz_sbmm(const dz_sbmm_args* args, void* stream) {
-  int rc = check_sbmm_args(args, false);
+  int rc = check_sbmm_args(args, false, true);
   if (rc || args->M == 0) return rc;
   return launch_sbmm(*args, false, (cudaStream_t)stream);
 }
 
 int dz_base_gemm(const dz_sbmm_args* args, void* stream) {
-  int rc = check_sbmm_args(args, true);
+  int rc = check_sbmm_args(args, true, true);
   if (rc || args->M == 0) return rc;
   return launch_sbmm(*args, true, (cudaStream_t)stream);
 }
 
 // Validation twin of dz_sbmm on CUDA cores (same arguments, no workspace use).
 int dz_sbmm_simt(const dz_sbmm_args* args, void* stream) {
-  int rc = check_sbmm_args(args, false);
+  int rc = check_sbmm_args(args, false, true);
   if (rc || args->M == 0) return rc;
   if (args->dtype != DZ_DTYPE_F16) return DZ_ERR_UNSUPPORTED;   // the twin is fp16 only
+  if (args->flags || (args->y_stride && args->y_stride != args->N) || !args->w_base)
+    return DZ_ERR_UNSUPPORTED;                                   // plain y = base + delta only
   return launch_sbmm_simt(*args, false, (cudaStream_t)stream);
 }
 

@@ -143,7 +143,24 @@ int launch_unpack(const void* sq, const void* sm, const uint16_t* ss, int N, int
                   uint16_t* out, cudaStream_t st);
 int launch_build_segments(const void* indices, int index_dtype, int M, int num_slots,
                           void* segments, cudaStream_t st);
+
+// ---------------------------------------------------------------------------
+// SBMM workspace: [status word | per-tile counters | parked split-K partials | gather buffer].
+// Shared by the launcher, the argument checks and the entry point with built-in scratch.
+// ---------------------------------------------------------------------------
+constexpr size_t kWsStatus = 0;            // int: first error a kernel met (sticky until read)
+constexpr size_t kWsCounters = 256;        // int[2 * tiles]: ticket / parked per tile
+constexpr size_t kWsCountersBytes = 16384;
+constexpr size_t kWsPartials = kWsCounters + kWsCountersBytes;
+constexpr int kMaxCtas = 160;              // upper bound of the SBMM grid (one CTA per SM)
+__host__ __device__ inline size_t sbmm_partial_bytes(int M) {
+  const int cols = M < 128 ? round_up(M, 16) : 128;
+  return (size_t)kMaxCtas * 2 * cols * 128 * sizeof(float);
+}
 size_t sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted);
+// Argument checks of dz_sbmm / dz_base_gemm; `check_workspace` = false for callers that
+// supply the scratch themselves.
+int check_sbmm_args(const dz_sbmm_args* a, bool base_only, bool check_workspace);
 int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st);
 
 }  // namespace dz

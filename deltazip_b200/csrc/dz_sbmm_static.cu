@@ -16,11 +16,13 @@
 //   * every GPU that loads the library holds kStaticBytes of device memory from
 //     load until process exit;
 //   * all calls on a device use the same array, which keeps whatever the last
-//     call left in it.  The status word and the tile counters are cleared at the
-//     start of every call (a memset on the caller's stream); the partial tiles
-//     are always written before they are read.  Two calls that overlap on the GPU
-//     (different streams, no ordering between them) race on the array and give
-//     undefined results -- order them.
+//     call left in it.  The tile counters are cleared at the start of every call
+//     (a memset on the caller's stream); the partial tiles are always written
+//     before they are read.  The status word is NOT cleared per call: what a
+//     kernel reports there (a rejected batch, a wait that ran out) stays until
+//     dz_sbmm_static_status reads and clears it.  Two calls that overlap on the
+//     GPU (different streams, no ordering between them) race on the array and
+//     give undefined results -- order them.
 #include <mutex>
 
 #include "dz_common.cuh"
@@ -29,9 +31,11 @@ namespace dz {
 namespace {
 
 constexpr int kStaticMaxTokens = 64;
-// status + counters (16640 B) and 160 CTAs x 2 partial tiles x 64 columns x 128 rows x 4 B
-constexpr size_t kStaticBytes = 16640 + (size_t)160 * 2 * kStaticMaxTokens * 128 * 4;
-constexpr size_t kStaticClearBytes = 16640;
+// status word + tile counters, then the parked partial tiles of a 64-token call
+constexpr size_t kStaticBytes = kWsPartials + (size_t)kMaxCtas * 2 * kStaticMaxTokens * 128 * 4;
+static_assert(kWsStatus + sizeof(int) <= kWsCounters, "status word precedes the counters");
+static_assert(kStaticMaxTokens % 16 == 0 && kStaticMaxTokens <= kTokenBlock,
+              "the partial area below is that of one token block of kStaticMaxTokens columns");
 
 // Device-resident scratch.  In host code this name is only a handle for the
 // runtime's symbol table, never a device address: the address the kernel gets
@@ -66,33 +70,37 @@ extern "C" int dz_sbmm_static_max_tokens(void) { return kStaticMaxTokens; }
 
 extern "C" int dz_sbmm_static(const dz_sbmm_args* args, void* stream) {
   if (!args) return DZ_ERR_INVALID_ARG;
-  if (args->M < 0) return DZ_ERR_INVALID_ARG;
-  if (args->M == 0) return DZ_OK;
   if (args->M > kStaticMaxTokens) return DZ_ERR_TOO_LARGE;   // scratch is sized for 64 tokens
-  if (!args->tokens_sorted) return DZ_ERR_TOO_LARGE;         // the gather buffer does not fit
-  if (!args->x || !args->w_base || !args->y || !args->qweight || !args->meta || !args->scales ||
-      !args->segments)
-    return DZ_ERR_INVALID_ARG;
-  if (args->N <= 0 || args->K <= 0) return DZ_ERR_INVALID_ARG;
-  if (args->N % kTileN != 0 || args->K % kBlockK != 0 || (args->bits != 2 && args->bits != 4))
-    return DZ_ERR_SHAPE;
-  if (args->dtype != DZ_DTYPE_F16 && args->dtype != DZ_DTYPE_BF16) return DZ_ERR_INVALID_ARG;
-  if (args->num_slots <= 0 || args->num_slots > kMaxSlots) return DZ_ERR_INVALID_ARG;
-  if (!aligned16(args->x) || !aligned16(args->w_base) || !aligned16(args->y) ||
-      !aligned16(args->qweight) || !aligned16(args->meta) || (args->qweight_stride & 15) ||
-      (args->meta_stride & 15) || (args->scales_stride & 1))
-    return DZ_ERR_ALIGNMENT;
+  if (args->M > 0 && !args->tokens_sorted) return DZ_ERR_TOO_LARGE;   // no room for a gather buffer
+  int rc = check_sbmm_args(args, false, /*check_workspace=*/false);   // same rules as dz_sbmm
+  if (rc || args->M == 0) return rc;
   if (sbmm_workspace_bytes(args->M, args->N, args->K, 1) > kStaticBytes) return DZ_ERR_TOO_LARGE;
 
   void* scratch = nullptr;
-  int rc = static_scratch_for_current_device(&scratch);   // first call on a device: set-up
+  rc = static_scratch_for_current_device(&scratch);   // first call on a device: set-up
   if (rc) return rc;
 
   cudaStream_t st = (cudaStream_t)stream;
-  // the status word and the tile counters must start at zero
-  DZ_CUDA_OK(cudaMemsetAsync(scratch, 0, kStaticClearBytes, st));
+  // the tile counters must start at zero; the status word before them is left alone
+  DZ_CUDA_OK(cudaMemsetAsync(static_cast<unsigned char*>(scratch) + kWsCounters, 0,
+                             kWsCountersBytes, st));
   dz_sbmm_args a = *args;
   a.workspace = scratch;
   a.workspace_bytes = kStaticBytes;
   return launch_sbmm(a, false, st);
+}
+
+// Reads and clears the status word of the built-in scratch on the current device.  Works on
+// the cached device address and a stack variable of the caller: no allocation.
+extern "C" int dz_sbmm_static_status(void* stream, int* host_out) {
+  if (!host_out) return DZ_ERR_INVALID_ARG;
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  int* word = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + kWsStatus);
+  DZ_CUDA_OK(cudaMemcpyAsync(host_out, word, sizeof(int), cudaMemcpyDeviceToHost, st));
+  DZ_CUDA_OK(cudaMemsetAsync(word, 0, sizeof(int), st));
+  DZ_CUDA_OK(cudaStreamSynchronize(st));
+  return DZ_OK;
 }

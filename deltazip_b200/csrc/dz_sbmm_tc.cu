@@ -44,7 +44,6 @@
 // from phase n + 2).
 #include <cuda.h>
 #include <cuda_bf16.h>
-#include <stdlib.h>
 
 #include <mutex>
 
@@ -71,10 +70,16 @@ constexpr int kMaxW = 4, kMaxX = 4, kMaxR = 16, kMaxBuf = 8;
 constexpr int kMaxWin = 128;                   // windows of one token block
 constexpr int kTmemCols = 512;
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
-constexpr int kMaxCtas = 160;
 constexpr int kSmemBudget = 216 * 1024;
 constexpr int kEpilogueUnits = 2;               // cost of a tile's epilogue in k-units (work split)
 constexpr int kPrefetchTiles = 8;               // W half-tiles prefetched to L2 in the prologue
+// Per-CTA wall-clock marks (8 x u64 per CTA in the upper part of the counter region) are
+// compiled in only with -DDZ_INSTRUMENT; the shipped kernel carries none.
+#ifdef DZ_INSTRUMENT
+constexpr bool kInstr = true;
+#else
+constexpr bool kInstr = false;
+#endif
 
 // TMEM columns: D_base [0, dcols), D_delta [dcols, 2 dcols), then 32 columns of
 // expanded A per buffer, then 4 columns of metadata per buffer.
@@ -86,7 +91,8 @@ struct Params {
   int num_kunits, num_tiles, num_kblocks;
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
   int base_only, delta_only, tokens_sorted;   // delta_only: no base product (w_base absent)
-  int debug;
+  int accumulate;                             // y += result
+  long long ldy;                              // elements between rows of y
   int grid, total_units, epi_units;   // total_units counts virtual units
   int w_stages, x_stages, r_per_class, xb_bytes;
   int nclass, dcols;
@@ -192,9 +198,16 @@ __device__ __forceinline__ uint32_t make_idesc(int n, bool sparse) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 template <int DT>
-__device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
-  if (DT == 0) reinterpret_cast<__half*>(y)[idx] = __float2half_rn(v);
-  else reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+__device__ __forceinline__ void store_out(void* y, size_t idx, float v, int accumulate) {
+  if (DT == 0) {
+    __half* o = reinterpret_cast<__half*>(y) + idx;
+    if (accumulate) v += __half2float(*o);
+    *o = __float2half_rn(v);
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(y) + idx;
+    if (accumulate) v += __bfloat162float(*o);
+    *o = __float2bfloat16_rn(v);
+  }
 }
 // Shared-memory matrix descriptors (K-major tile, 128-byte swizzle, rows 128 B
 // apart, 8-row groups 1024 B apart) are handled as (lo, hi) 32-bit halves: hi
@@ -429,7 +442,7 @@ struct Ring {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int BITS, int DT, bool INSTR>
+template <int BITS, int DT>
 __global__ void __launch_bounds__(kThreads, 1)
 sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xc,
                const Params p) {
@@ -441,8 +454,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ int s_abort, s_last, s_npre;
   __shared__ uint32_t s_fixpar[kNumWG];
 
-  // INSTR only: per-CTA wall-clock marks of the last launch (8 x u64 per CTA) in the upper
-  // part of the counter region
+  constexpr bool INSTR = kInstr;
   unsigned long long* const tl =
       reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.counters) + 4096) +
       (size_t)blockIdx.x * 8;
@@ -952,8 +964,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               }
             }
             // the tile is settled once this fragment has written it: counters back to zero
-            p.counters[2 * tile] = 0;
-            p.counters[2 * tile + 1] = 0;
+            // (not after a timeout: late fragments may still add to them, and the caller
+            // has to clear the workspace after DZ_ERR_TIMEOUT anyway)
+            if (!*abort_flag) {
+              p.counters[2 * tile] = 0;
+              p.counters[2 * tile + 1] = 0;
+            }
           }
           s_last = is_last;
         }
@@ -1019,7 +1035,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const int cnt = min(3, nfrag - 1 - j);
               if (j > 0) named_bar_sync(2 + wg, 128);
               if (wg_tid == 0) {
+                // the scratch was written by generic stores (shared), the parked partials by
+                // other CTAs' generic stores (global): both must be ordered before the bulk
+                // copies, which go through the async proxy
                 fence_proxy_async();
+                asm volatile("fence.proxy.async.global;" ::: "memory");
                 mbar_expect_tx(fixbar, cnt * 4096);
 #pragma unroll
                 for (int ff = 0; ff < 3; ++ff) {
@@ -1063,7 +1083,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const int prow = p.row0 + col + i;
               if (prow < p.M) {
                 const int tok = perm ? perm[prow] : prow;
-                store_out<DT>(p.y, (size_t)tok * p.N + n0 + r, __uint_as_float(v[i]));
+                store_out<DT>(p.y, (size_t)tok * (size_t)p.ldy + n0 + r, __uint_as_float(v[i]),
+                              p.accumulate);
               }
             }
           } else {
@@ -1193,28 +1214,18 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows, i
 
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[6] = {false, false, false, false, false, false};
+  bool attr_set[4] = {false, false, false, false};
 };
 DeviceInfo& device_info(int dev) {
   static DeviceInfo info[64];
   return info[dev & 63];
 }
 
-constexpr size_t kWsStatus = 0;
-constexpr size_t kWsCounters = 256;
-constexpr size_t kWsCountersBytes = 16384;
-constexpr size_t kWsPartials = kWsCounters + kWsCountersBytes;
-
-inline size_t partial_bytes(int M) {
-  const int cols = min(kTokenBlock, round_up(M, 16));
-  return (size_t)kMaxCtas * 2 * cols * 128 * sizeof(float);
-}
-
 }  // namespace
 
 size_t sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  size_t b = kWsPartials + partial_bytes(M);
+  size_t b = kWsPartials + sbmm_partial_bytes(M);
   if (!tokens_sorted) b += (size_t)round_up(M, 16) * K * 2 + 1024;
   return b;
 }
@@ -1230,7 +1241,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   const bool sorted = base_only || a.tokens_sorted != 0;
   const void* xsrc = a.x;
   if (!sorted) {
-    uint8_t* xs = ws + ((kWsPartials + partial_bytes(a.M) + 1023) & ~(size_t)1023);
+    uint8_t* xs = ws + ((kWsPartials + sbmm_partial_bytes(a.M) + 1023) & ~(size_t)1023);
     gather_rows_kernel<<<a.M, 128, 0, st>>>((const uint4*)a.x, (const uint8_t*)a.segments,
                                              (uint4*)xs, a.M, a.K / 8);
     DZ_CUDA_OK(cudaGetLastError());
@@ -1256,7 +1267,8 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.num_tiles = a.N / kTileN;
   p.base_only = base_only ? 1 : 0;
   p.delta_only = (!base_only && a.w_base == nullptr) ? 1 : 0;
-  { const char* e = getenv("DZ_DEBUG"); p.debug = e ? atoi(e) : 0; }
+  p.accumulate = (a.flags & DZ_SBMM_ACCUMULATE) ? 1 : 0;
+  p.ldy = a.y_stride ? a.y_stride : a.N;
   p.tokens_sorted = sorted ? 1 : 0;
   p.epi_units = kEpilogueUnits;
   p.total_units = p.num_tiles * (p.num_kunits + p.epi_units);
@@ -1272,10 +1284,7 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.counters = reinterpret_cast<int*>(ws + kWsCounters);
   p.partials = reinterpret_cast<float*>(ws + kWsPartials);
 
-  const bool instr = (p.debug & 16) != 0;
-  const int dtq = (a.dtype == DZ_DTYPE_BF16) ? 1 : 0;
-  if (instr && dtq) return DZ_ERR_UNSUPPORTED;
-  const int kidx = ((a.bits == 2) ? 0 : 1) + (instr ? 2 : (dtq ? 4 : 0));
+  const int kidx = ((a.bits == 2) ? 0 : 1) + (dt ? 2 : 0);
   const int num_tb = (a.M + kTokenBlock - 1) / kTokenBlock;
   for (int tb = 0; tb < num_tb; ++tb) {
     p.token_block = tb;
@@ -1292,9 +1301,8 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols, dt);
     if (rc) return rc;
     const size_t smem = (size_t)fixed + (size_t)p.nclass * p.r_per_class * kRStage + 1024;
-    auto kern = instr ? ((a.bits == 2) ? sbmm_tc_kernel<2, 0, true> : sbmm_tc_kernel<4, 0, true>)
-                : dt  ? ((a.bits == 2) ? sbmm_tc_kernel<2, 1, false> : sbmm_tc_kernel<4, 1, false>)
-                      : ((a.bits == 2) ? sbmm_tc_kernel<2, 0, false> : sbmm_tc_kernel<4, 0, false>);
+    auto kern = dt ? ((a.bits == 2) ? sbmm_tc_kernel<2, 1> : sbmm_tc_kernel<4, 1>)
+                   : ((a.bits == 2) ? sbmm_tc_kernel<2, 0> : sbmm_tc_kernel<4, 0>);
     if (!di.attr_set[kidx]) {
       DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
       di.attr_set[kidx] = true;

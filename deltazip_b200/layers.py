@@ -21,7 +21,7 @@ from . import ops
 from .config import DeltaConfig
 from .custom_all_reduce import get_handle as get_custom_ar_handle
 from .parallel_state import (get_tensor_model_parallel_rank, get_tensor_model_parallel_world_size,
-                             shard_range, tensor_model_parallel_all_gather,
+                             SHARD_UNIT, shard_range, tensor_model_parallel_all_gather,
                              tensor_model_parallel_all_reduce)
 
 ASYNC_COPY = True
@@ -61,7 +61,7 @@ class ColumnParallelLinear(_ParallelLinearBase):
     def __init__(self, input_size: int, output_size: int, full_weight: Optional[torch.Tensor] = None,
                  gather_output: bool = False, device="cuda", dtype=torch.float16):
         rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
-        lo, hi = shard_range(output_size, 128, rank, size)
+        lo, hi = shard_range(output_size, SHARD_UNIT, rank, size)
         if full_weight is None:
             w = torch.empty((hi - lo, input_size), dtype=dtype, device=device).normal_(0, 0.02)
         else:
@@ -85,7 +85,7 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
         rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
         parts, self.shards = [], []
         for i, out in enumerate(output_sizes):
-            lo, hi = shard_range(out, 128, rank, size)
+            lo, hi = shard_range(out, SHARD_UNIT, rank, size)
             self.shards.append((lo, hi))
             if full_weights is None:
                 parts.append(torch.empty((hi - lo, input_size), dtype=dtype, device=device).normal_(0, 0.02))
@@ -114,14 +114,14 @@ class QKVParallelLinear(MergedColumnParallelLinear):
 
 
 class RowParallelLinear(_ParallelLinearBase):
-    """y = x W^T with W split along the input dimension (whole 64-column blocks per rank),
-    partial results summed over the ranks."""
+    """y = x W^T with W split along the input dimension at the same 128-wide boundaries as the
+    column-parallel layer that produces x, partial results summed over the ranks."""
 
     def __init__(self, input_size: int, output_size: int, full_weight: Optional[torch.Tensor] = None,
                  input_is_parallel: bool = True, reduce_results: bool = True, device="cuda",
                  dtype=torch.float16):
         rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
-        lo, hi = shard_range(input_size, 64, rank, size)
+        lo, hi = shard_range(input_size, SHARD_UNIT, rank, size)
         if full_weight is None:
             w = torch.empty((output_size, hi - lo), dtype=dtype, device=device).normal_(0, 0.02)
         else:
@@ -160,15 +160,23 @@ class BaseLayerWithDelta(nn.Module):
 
     # -- slots ---------------------------------------------------------------
     def create_delta_weights(self, max_deltas: int, delta_config: DeltaConfig,
-                             model_config=None) -> None:
-        """Allocates zeroed slot stacks: qweight int32 [D, K*b/128, 2N], scales fp16 [D, 1, N],
-        meta int16 [D, N, K/16] for this rank's weight shard [N, K]."""
+                             model_config=None, storage=None) -> None:
+        """Slot stacks of this rank's weight shard [N, K]: qweight int32 [D, K*b/128, 2N], scales
+        fp16 [D, 1, N], meta int16 [D, N, K/16].  Allocated (zeroed) here, or taken from
+        `storage` = (qweight, meta, scales) when a manager carves them out of its slot arena
+        (slots may then be any number of bytes apart; the kernel takes the strides)."""
         n, k = self.base_layer.weight.shape
         self.bits = delta_config.max_bitwidth
         self.pack_factor = delta_config.pack_factor
         self.bitwidth = [0] * max_deltas
-        self.qweight_stacked, self.meta_stacked, self.scales_stacked = ops.alloc_slots(
-            max_deltas, n, k, self.bits, self.base_layer.weight.device)
+        if storage is None:
+            storage = ops.alloc_slots(max_deltas, n, k, self.bits, self.base_layer.weight.device)
+        else:
+            want = ops.slot_shapes(n, k, self.bits)
+            for t, shape in zip(storage, want):
+                if tuple(t.shape) != (max_deltas, *shape):
+                    raise ValueError(f"slot storage {tuple(t.shape)} does not match {(max_deltas, *shape)}")
+        self.qweight_stacked, self.meta_stacked, self.scales_stacked = storage
 
     def reset_delta(self, index: int):
         self.bitwidth[index] = 0
@@ -211,7 +219,7 @@ class BaseLayerWithDelta(nn.Module):
     def apply_weights(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if bias is not None:
-            raise ValueError("delta layers do not support bias yet.")
+            raise ValueError("bias is not supported by the delta layers")
         w = self.base_layer.linear_weights["weight"]
         if self.segments is not None:
             return ops.sbmm(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
@@ -250,11 +258,11 @@ class MergedColumnParallelLinearWithDelta(ColumnParallelLinearWithDelta):
     """gate_proj + up_proj: one delta tensor set covers both slices (the checkpoint stores the
     merged, per-rank pre-sharded matrix, as the reference's converter writes it)."""
 
-    def create_delta_weights(self, max_deltas, delta_config, model_config=None):
+    def create_delta_weights(self, max_deltas, delta_config, model_config=None, storage=None):
         sizes = self.base_layer.output_sizes
         if not (len(sizes) == 2 and sizes[0] == sizes[1]):
-            raise ValueError("DeltaColumnParallelLinear2Slice requires 2 slices with the same size.")
-        super().create_delta_weights(max_deltas, delta_config, model_config)
+            raise ValueError("a merged gate/up delta layer needs two output slices of equal width")
+        super().create_delta_weights(max_deltas, delta_config, model_config, storage)
 
     @classmethod
     def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
@@ -262,10 +270,10 @@ class MergedColumnParallelLinearWithDelta(ColumnParallelLinearWithDelta):
 
 
 class MergedQKVParallelLinearWithDelta(ColumnParallelLinearWithDelta):
-    def create_delta_weights(self, max_deltas, delta_config, model_config=None):
+    def create_delta_weights(self, max_deltas, delta_config, model_config=None, storage=None):
         self.q_proj_shard_size = self.base_layer.num_heads * self.base_layer.head_size
         self.kv_proj_shard_size = self.base_layer.num_kv_heads * self.base_layer.head_size
-        super().create_delta_weights(max_deltas, delta_config, model_config)
+        super().create_delta_weights(max_deltas, delta_config, model_config, storage)
 
     @classmethod
     def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
@@ -306,12 +314,14 @@ _all_delta_classes = (MergedQKVParallelLinearWithDelta, MergedColumnParallelLine
 
 
 def from_layer(layer: nn.Module, max_deltas: int, delta_config: DeltaConfig,
-               packed_modules_list: List, model_config=None) -> nn.Module:
+               packed_modules_list: List, model_config=None, allocate: bool = True) -> nn.Module:
     """Wraps `layer` in the matching delta layer and allocates its slots (returns `layer`
-    unchanged when no delta class applies)."""
+    unchanged when no delta class applies).  With `allocate=False` the caller provides the slot
+    storage afterwards through create_delta_weights(..., storage=...)."""
     for cls in _all_delta_classes:
         if cls.can_replace_layer(layer, delta_config, packed_modules_list, model_config):
             ret = cls(layer)
-            ret.create_delta_weights(max_deltas, delta_config, model_config)
+            if allocate:
+                ret.create_delta_weights(max_deltas, delta_config, model_config)
             return ret
     return layer

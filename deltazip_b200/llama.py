@@ -1,23 +1,28 @@
 """A minimal Llama decoder over the delta linear layers: the harness that drives the SBMM
 path the way the reference's model code does (serving/vllm/model_executor/models/llama.py
-:59-235: qkv_proj -> rotary attention -> o_proj, gate_up_proj -> SiLU*up -> down_proj, RMSNorm,
-module names and `supported_delta_modules` / `packed_modules_mapping` as in :299-327).
+:59-235: qkv_proj -> rotary attention -> o_proj, gate_up_proj -> SiLU*up -> down_proj, RMSNorm
+with the residual carried beside the hidden state, module names and `supported_delta_modules` /
+`packed_modules_mapping` as in :299-327), tensor parallel over the ranks of parallel_state.
 
-Only the four projections per layer are this library's work; attention, norms, rotary and the
-sampler are plain PyTorch (they are not on the hot path).  Sequences advance in lock step with
-a dense per-sequence KV cache, which is enough to check greedy decoding against the reference's
-PyTorch dequantise-then-matmul path on random-init weights and to time decode steps.
+A decode step is a chain of this library's launches: per layer rmsnorm (+ residual add), qkv
+SBMM, rotary + paged-cache write, paged decode attention, o SBMM (+ all-reduce), rmsnorm, gate_up
+SBMM, SiLU*up, down SBMM (+ all-reduce).  Prefill runs the same linears over all prompt tokens
+and uses PyTorch's attention on the fresh q/k/v (prefill attention is not on the path).
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional
+from typing import Callable, List, Optional, Sequence
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
 from . import layers as L
+from . import ops
+from .parallel_state import (SHARD_UNIT, get_tensor_model_parallel_rank,
+                             get_tensor_model_parallel_world_size, shard_range)
 
 
 @dataclass
@@ -35,36 +40,71 @@ class LlamaConfig:
     def head_dim(self) -> int:
         return self.hidden_size // self.num_attention_heads
 
+    @property
+    def kv_heads(self) -> int:
+        return self.num_key_value_heads or self.num_attention_heads
 
-def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+LLAMA2_7B = LlamaConfig(4096, 11008, 32, 32, None)
+LLAMA2_13B = LlamaConfig(5120, 13824, 40, 40, None)
+LLAMA2_70B = LlamaConfig(8192, 28672, 80, 64, 8)
 
 
-def rotary(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
-    """x: [B, T, H, D] (neox style, halves rotated), positions: [B, T]."""
-    d = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
-    ang = positions.float()[..., None] * inv                      # [B, T, D/2]
-    cos, sin = ang.cos()[:, :, None, :], ang.sin()[:, :, None, :]
-    x1, x2 = x.float()[..., : d // 2], x.float()[..., d // 2:]
-    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+class PagedKVCache:
+    """Per-layer K and V pools of `num_blocks` blocks of `block_size` tokens, [slots, kv_heads,
+    128] each, with a free list (role of the reference's block manager + cache engine,
+    serving/vllm/core/block_manager.py, serving/vllm/worker/cache_engine.py, reduced to what a
+    single process needs)."""
+
+    def __init__(self, num_layers: int, num_blocks: int, kv_heads: int, block_size: int = 16,
+                 dtype=torch.float16, device="cuda"):
+        self.block_size, self.num_blocks, self.kv_heads = block_size, num_blocks, kv_heads
+        shape = (num_blocks * block_size, kv_heads, 128)
+        self.k = [torch.empty(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self.v = [torch.empty(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self.free: List[int] = list(range(num_blocks - 1, -1, -1))
+
+    def allocate(self, n_blocks: int) -> List[int]:
+        if n_blocks > len(self.free):
+            raise RuntimeError("out of KV cache blocks")
+        return [self.free.pop() for _ in range(n_blocks)]
+
+    def release(self, blocks: Sequence[int]) -> None:
+        self.free.extend(blocks)
+
+    def slots(self, blocks: Sequence[int], start: int, count: int) -> List[int]:
+        """Cache slots of token positions [start, start + count) of a sequence owning `blocks`."""
+        bs = self.block_size
+        return [blocks[p // bs] * bs + p % bs for p in range(start, start + count)]
+
+
+@dataclass
+class AttnMeta:
+    """How attention runs in one forward pass.  Decode: `block_tables` [B, max_blocks] int32 and
+    `seq_lens` [B] int32 (cached length including the current token).  Prefill: `prompt_lens`,
+    the token count of each sequence, rows in (sequence, position) order."""
+    slot_mapping: Optional[torch.Tensor] = None          # int64 [M] cache slot per token, -1 = none
+    block_tables: Optional[torch.Tensor] = None
+    seq_lens: Optional[torch.Tensor] = None
+    prompt_lens: Optional[List[int]] = None
+    splits: int = 1
 
 
 class LlamaDecoderLayer(nn.Module):
-    def __init__(self, cfg: LlamaConfig, device="cuda"):
+    def __init__(self, cfg: LlamaConfig, device="cuda", dtype=torch.float16):
         super().__init__()
-        kv = cfg.num_key_value_heads or cfg.num_attention_heads
         self.cfg = cfg
         self.qkv_proj = L.QKVParallelLinear(cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads,
-                                            kv, device=device)
-        self.o_proj = L.RowParallelLinear(cfg.hidden_size, cfg.hidden_size, device=device)
+                                            cfg.kv_heads, device=device, dtype=dtype)
+        self.o_proj = L.RowParallelLinear(cfg.hidden_size, cfg.hidden_size, device=device, dtype=dtype)
         self.gate_up_proj = L.MergedColumnParallelLinear(
-            cfg.hidden_size, [cfg.intermediate_size, cfg.intermediate_size], device=device)
-        self.down_proj = L.RowParallelLinear(cfg.intermediate_size, cfg.hidden_size, device=device)
-        self.input_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=torch.float16, device=device))
+            cfg.hidden_size, [cfg.intermediate_size, cfg.intermediate_size], device=device, dtype=dtype)
+        self.down_proj = L.RowParallelLinear(cfg.intermediate_size, cfg.hidden_size, device=device,
+                                             dtype=dtype)
+        self.input_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device),
+                                            requires_grad=False)
         self.post_attention_layernorm = nn.Parameter(
-            torch.ones(cfg.hidden_size, dtype=torch.float16, device=device))
+            torch.ones(cfg.hidden_size, dtype=dtype, device=device), requires_grad=False)
 
 
 class LlamaForCausalLM(nn.Module):
@@ -72,18 +112,33 @@ class LlamaForCausalLM(nn.Module):
     packed_modules_mapping = {"qkv_proj": ["q_proj", "k_proj", "v_proj"],
                               "gate_up_proj": ["gate_proj", "up_proj"]}
 
-    def __init__(self, cfg: LlamaConfig, device="cuda", seed: int = 0):
+    def __init__(self, cfg: LlamaConfig, device="cuda", seed: int = 0, dtype=torch.float16):
         super().__init__()
         self.cfg = cfg
+        self.dtype = dtype
+        self.tp_size = get_tensor_model_parallel_world_size()
+        self.tp_rank = get_tensor_model_parallel_rank()
+        if cfg.head_dim != 128:
+            raise ValueError("the decode kernels take head size 128 (every Llama-2 size)")
+        if cfg.num_attention_heads % self.tp_size:
+            raise ValueError("attention heads must divide by the tensor-parallel size")
+        self.q_heads = cfg.num_attention_heads // self.tp_size
+        self.kv_heads = max(1, cfg.kv_heads // self.tp_size)
         g = torch.Generator(device=device).manual_seed(seed)
         self.embed_tokens = nn.Parameter(
-            torch.empty((cfg.vocab_size, cfg.hidden_size), dtype=torch.float16, device=device).normal_(
+            torch.empty((cfg.vocab_size, cfg.hidden_size), dtype=dtype, device=device).normal_(
                 0, 1.0, generator=g), requires_grad=False)
-        self.layers = nn.ModuleList([LlamaDecoderLayer(cfg, device) for _ in range(cfg.num_hidden_layers)])
-        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=torch.float16, device=device))
-        self.lm_head = nn.Parameter(
-            torch.empty((cfg.vocab_size, cfg.hidden_size), dtype=torch.float16, device=device).normal_(
-                0, 0.05, generator=g), requires_grad=False)
+        self.layers = nn.ModuleList([LlamaDecoderLayer(cfg, device, dtype)
+                                     for _ in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device),
+                                 requires_grad=False)
+        # vocab-parallel output matrix: this rank's rows [v_lo, v_hi)
+        full = torch.empty((cfg.vocab_size, cfg.hidden_size), dtype=dtype, device=device).normal_(
+            0, 0.05, generator=g)
+        self.v_lo, self.v_hi = shard_range(cfg.vocab_size, SHARD_UNIT, self.tp_rank, self.tp_size) \
+            if cfg.vocab_size % SHARD_UNIT == 0 else (0, cfg.vocab_size)
+        self.lm_head = nn.Parameter(full[self.v_lo:self.v_hi].contiguous(), requires_grad=False)
+        del full
         # a custom linear hook lets the same model run the reference's PyTorch path
         self.linear_override: Optional[Callable[[str, nn.Module, torch.Tensor], torch.Tensor]] = None
 
@@ -92,72 +147,112 @@ class LlamaForCausalLM(nn.Module):
             return self.linear_override(name, module, x)
         return module(x)[0]
 
-    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, kv_cache: List[Dict],
-                cache_len: int) -> torch.Tensor:
-        """tokens, positions: [B, T]; kv_cache[layer] = {"k","v"}: [B, Hkv, Tmax, D]; returns the
-        hidden states [B, T, hidden] after the final norm.  The B*T token rows are handed to the
-        linear layers in (sequence, position) order."""
+    # -- attention ---------------------------------------------------------------
+    def _attention(self, li: int, qkv: torch.Tensor, positions: torch.Tensor,
+                   cache: Optional[PagedKVCache], meta: AttnMeta) -> torch.Tensor:
         cfg = self.cfg
-        b, t = tokens.shape
-        h = self.embed_tokens[tokens]                                  # [B, T, hidden]
-        hkv = cfg.num_key_value_heads or cfg.num_attention_heads
-        for li, layer in enumerate(self.layers):
-            x = rms_norm(h, layer.input_layernorm, cfg.rms_norm_eps).reshape(b * t, -1)
-            qkv = self._linear(f"layers.{li}.qkv_proj", layer.qkv_proj, x).reshape(b, t, -1)
-            qd, kd = cfg.num_attention_heads * cfg.head_dim, hkv * cfg.head_dim
-            q = rotary(qkv[..., :qd].reshape(b, t, cfg.num_attention_heads, cfg.head_dim), positions,
-                       cfg.rope_theta)
-            k = rotary(qkv[..., qd:qd + kd].reshape(b, t, hkv, cfg.head_dim), positions, cfg.rope_theta)
-            v = qkv[..., qd + kd:].reshape(b, t, hkv, cfg.head_dim)
-            kc, vc = kv_cache[li]["k"], kv_cache[li]["v"]
-            kc[:, :, cache_len:cache_len + t] = k.transpose(1, 2)
-            vc[:, :, cache_len:cache_len + t] = v.transpose(1, 2)
-            keys, vals = kc[:, :, :cache_len + t], vc[:, :, :cache_len + t]
-            if hkv != cfg.num_attention_heads:
-                rep = cfg.num_attention_heads // hkv
-                keys, vals = keys.repeat_interleave(rep, dim=1), vals.repeat_interleave(rep, dim=1)
-            mask = None
-            if t > 1:
-                mask = torch.ones(t, cache_len + t, dtype=torch.bool, device=tokens.device).tril(cache_len)
-            att = F.scaled_dot_product_attention(q.transpose(1, 2), keys, vals, attn_mask=mask)
-            att = att.transpose(1, 2).reshape(b * t, -1)
-            h = h + self._linear(f"layers.{li}.o_proj", layer.o_proj, att).reshape(b, t, -1)
-            x = rms_norm(h, layer.post_attention_layernorm, cfg.rms_norm_eps).reshape(b * t, -1)
-            gu = self._linear(f"layers.{li}.gate_up_proj", layer.gate_up_proj, x)
-            half = gu.shape[-1] // 2
-            act = F.silu(gu[:, :half]) * gu[:, half:]
-            h = h + self._linear(f"layers.{li}.down_proj", layer.down_proj, act).reshape(b, t, -1)
-        return rms_norm(h, self.norm, cfg.rms_norm_eps)
+        kc = cache.k[li] if cache is not None else None
+        vc = cache.v[li] if cache is not None else None
+        ops.rotary_and_cache(qkv, positions, self.q_heads, self.kv_heads, cfg.rope_theta, kc, vc,
+                             meta.slot_mapping if cache is not None else None)
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        if meta.prompt_lens is None:
+            return ops.paged_attention_decode(qkv, kc, vc, meta.block_tables, meta.seq_lens,
+                                              self.q_heads, self.kv_heads, cache.block_size, scale,
+                                              splits=meta.splits)
+        # prefill: causal attention of every prompt over its own fresh keys / values
+        qd, kd = self.q_heads * 128, self.kv_heads * 128
+        out = torch.empty((qkv.shape[0], qd), dtype=qkv.dtype, device=qkv.device)
+        row = 0
+        for t in meta.prompt_lens:
+            blk = qkv[row:row + t]
+            q = blk[:, :qd].reshape(t, self.q_heads, 128).transpose(0, 1)[None]
+            k = blk[:, qd:qd + kd].reshape(t, self.kv_heads, 128).transpose(0, 1)[None]
+            v = blk[:, qd + kd:].reshape(t, self.kv_heads, 128).transpose(0, 1)[None]
+            if self.kv_heads != self.q_heads:
+                rep = self.q_heads // self.kv_heads
+                k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+            att = F.scaled_dot_product_attention(q, k, v, is_causal=t > 1, scale=scale)
+            out[row:row + t] = att[0].transpose(0, 1).reshape(t, qd)
+            row += t
+        return out
 
+    # -- forward -------------------------------------------------------------------
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, cache: Optional[PagedKVCache],
+                meta: AttnMeta) -> torch.Tensor:
+        """tokens, positions: [M] (int64); returns the hidden states [M, hidden] after the final
+        norm.  Token rows are handed to the linear layers in the order given."""
+        cfg = self.cfg
+        eps = cfg.rms_norm_eps
+        residual = self.embed_tokens[tokens]                            # [M, hidden]
+        x = ops.rms_norm(residual, self.layers[0].input_layernorm, eps)
+        for li, layer in enumerate(self.layers):
+            if li > 0:
+                x = ops.rms_norm(x, layer.input_layernorm, eps, residual=residual)
+            qkv = self._linear(f"layers.{li}.qkv_proj", layer.qkv_proj, x)
+            att = self._attention(li, qkv, positions, cache, meta)
+            assert att.shape[-1] == layer.o_proj.weight.shape[1], "qkv shard does not feed o_proj's K"
+            o = self._linear(f"layers.{li}.o_proj", layer.o_proj, att)
+            x = ops.rms_norm(o, layer.post_attention_layernorm, eps, residual=residual)
+            gu = self._linear(f"layers.{li}.gate_up_proj", layer.gate_up_proj, x)
+            act = ops.silu_and_mul(gu)
+            assert act.shape[-1] == layer.down_proj.weight.shape[1], \
+                "gate/up shard does not feed down_proj's K"
+            x = self._linear(f"layers.{li}.down_proj", layer.down_proj, act)
+        return ops.rms_norm(x, self.norm, eps, residual=residual)
+
+    # -- sampling --------------------------------------------------------------------
     def logits(self, hidden_last: torch.Tensor) -> torch.Tensor:
-        """fp32 logits of the last position of every sequence (sampler math, not the hot path)."""
+        """fp32 logits over this rank's vocabulary rows (sampler math, not the hot path)."""
         return hidden_last.float() @ self.lm_head.float().t()
 
-    def new_kv_cache(self, batch: int, max_len: int):
-        hkv = self.cfg.num_key_value_heads or self.cfg.num_attention_heads
-        dev = self.embed_tokens.device
-        return [{"k": torch.zeros((batch, hkv, max_len, self.cfg.head_dim), dtype=torch.float16, device=dev),
-                 "v": torch.zeros((batch, hkv, max_len, self.cfg.head_dim), dtype=torch.float16, device=dev)}
-                for _ in self.layers]
+    def greedy_tokens(self, hidden_last: torch.Tensor) -> torch.Tensor:
+        """argmax over the whole vocabulary: the output matrix runs on the dense tcgen05 GEMM,
+        each rank reduces its own vocabulary rows and the (value, index) pairs are exchanged
+        (the reference gathers full logits to rank 0 instead,
+        serving/vllm/delta/layers_marlin.py:696-711)."""
+        logits = ops.base_gemm(hidden_last, self.lm_head) if self.lm_head.shape[0] % 128 == 0 \
+            else (hidden_last @ self.lm_head.t())
+        val, idx = logits.float().max(dim=-1)
+        idx = idx + self.v_lo
+        if self.tp_size == 1:
+            return idx
+        import torch.distributed as dist
+        pair = torch.stack([val, idx.float()], dim=-1).contiguous()
+        parts = [torch.empty_like(pair) for _ in range(self.tp_size)]
+        dist.all_gather(parts, pair)
+        allp = torch.stack(parts)                                       # [tp, B, 2]
+        best = allp[:, :, 0].argmax(dim=0)
+        return allp[best, torch.arange(pair.shape[0], device=pair.device), 1].long()
 
 
 @torch.inference_mode()
 def greedy_generate(model: LlamaForCausalLM, prompts: torch.Tensor, steps: int,
-                    set_mapping: Callable[[int], None]) -> torch.Tensor:
+                    set_mapping: Callable[[int], None], block_size: int = 16) -> torch.Tensor:
     """Prefill `prompts` [B, T] then `steps` greedy decode steps; `set_mapping(tokens_per_seq)`
-    installs the per-token delta mapping for a forward pass with that many tokens per sequence.
-    Returns the generated ids [B, steps]."""
+    installs the per-token delta mapping for a forward pass with that many tokens per sequence
+    (rows in sequence-major order).  Returns the generated ids [B, steps]."""
     b, t = prompts.shape
-    kv = model.new_kv_cache(b, t + steps)
-    pos = torch.arange(t, device=prompts.device)[None, :].expand(b, t)
+    dev = prompts.device
+    blocks_per_seq = (t + steps + block_size - 1) // block_size
+    cache = PagedKVCache(len(model.layers), b * blocks_per_seq, model.kv_heads, block_size,
+                         model.dtype, dev)
+    tables = [cache.allocate(blocks_per_seq) for _ in range(b)]
+    block_tables = torch.tensor(tables, dtype=torch.int32, device=dev)
+    slots = torch.tensor([cache.slots(tb, 0, t) for tb in tables], dtype=torch.int64, device=dev)
+    pos = torch.arange(t, device=dev)[None, :].expand(b, t)
     set_mapping(t)
-    h = model(prompts, pos, kv, 0)
-    nxt = model.logits(h[:, -1]).argmax(-1)
+    h = model(prompts.reshape(-1), pos.reshape(-1).contiguous(), cache,
+              AttnMeta(slot_mapping=slots.reshape(-1), prompt_lens=[t] * b))
+    nxt = model.logits(h.reshape(b, t, -1)[:, -1]).argmax(-1)
     out = [nxt]
     set_mapping(1)
     for s in range(1, steps):
-        pos = torch.full((b, 1), t + s - 1, device=prompts.device, dtype=torch.long)
-        h = model(nxt[:, None], pos, kv, t + s - 1)
-        nxt = model.logits(h[:, -1]).argmax(-1)
+        cur = t + s - 1                                                  # position of the token fed in
+        pos1 = torch.full((b,), cur, device=dev, dtype=torch.int64)
+        slot1 = torch.tensor([cache.slots(tb, cur, 1)[0] for tb in tables], dtype=torch.int64, device=dev)
+        lens = torch.full((b,), cur + 1, device=dev, dtype=torch.int32)
+        h = model(nxt, pos1, cache, AttnMeta(slot_mapping=slot1, block_tables=block_tables, seq_lens=lens))
+        nxt = model.logits(h).argmax(-1)
         out.append(nxt)
     return torch.stack(out, dim=1)

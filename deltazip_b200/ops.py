@@ -105,12 +105,15 @@ class Segments:
         nbytes = lib().dz_segments_bytes(self.max_tokens, self.num_slots)
         self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         self.m = 0
-        self.sorted = True
+        self.sorted = False
 
     def build(self, indices: torch.Tensor, sorted_hint: Optional[bool] = None) -> "Segments":
-        """Builds the table on the current stream.  `sorted_hint` says whether
-        `indices` is non-decreasing (the reference's scheduler delivers batches
-        sorted by delta id); None checks on the device (one host sync)."""
+        """Builds the table on the current stream; never synchronises with the host.
+        `sorted_hint=True` is the caller's promise that `indices` is non-decreasing (the
+        reference's scheduler delivers batches sorted by delta id,
+        serving/vllm/core/scheduler.py:101-104): x is then read in place.  Without the
+        promise the SBMM first gathers x into sorted order on the device (a plain copy when
+        the batch happens to be sorted), so any order is handled."""
         _need_cuda(indices)
         m = indices.numel()
         if m > self.max_tokens:
@@ -125,13 +128,12 @@ class Segments:
         check(lib().dz_build_segments(indices.data_ptr(), dt, m, self.num_slots,
                                       self.buf.data_ptr(), _stream()), "dz_build_segments")
         self.m = m
-        if sorted_hint is None:
-            # same clamping as the device builder: ids outside [-1, num_slots) count as -1
-            c = torch.where((indices >= self.num_slots) | (indices < -1),
-                            torch.full_like(indices, -1), indices)
-            sorted_hint = bool(m < 2 or (c[1:] >= c[:-1]).all().item())
         self.sorted = bool(sorted_hint)
         return self
+
+    def is_sorted_on_device(self) -> bool:
+        """What the device-side builder found (synchronises; for tests and diagnostics)."""
+        return bool(self.header()[3])
 
     def header(self):
         """(M, num_slots, num_token_blocks, sorted, status, num_windows, num_active) -- syncs."""
@@ -182,9 +184,11 @@ def _bits_from_shapes(qweight_stacked: torch.Tensor, k: int) -> int:
 def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
          meta_stacked: torch.Tensor, segments: Segments, base_weight: Optional[torch.Tensor],
          out: Optional[torch.Tensor] = None, bits: Optional[int] = None,
-         _entry: str = "dz_sbmm") -> torch.Tensor:
+         _entry: str = "dz_sbmm", accumulate: bool = False) -> torch.Tensor:
     """y = x W^T + x dequant(delta_slot(i))^T with a prebuilt segment table.  With
-    `base_weight=None` only the delta products are computed (rows of slot -1 get 0)."""
+    `base_weight=None` only the delta products are computed (rows of slot -1 get 0).
+    `out` may be a column slice [:, a:a+N] of a wider row-major tensor; with
+    `accumulate=True` the result is added to `out` inside the kernel."""
     _need_cuda(x, qweight_stacked, scales_stacked, meta_stacked)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
@@ -202,9 +206,15 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
     if bits is None:
         bits = _bits_from_shapes(qweight_stacked, k)
     if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs the tensor to add to (out)")
         out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    out2 = out.reshape(-1, out.shape[-1]) if out.dim() != 2 else out
+    if out2.shape != (m, n) or out2.stride(1) != 1 or out2.dtype != x.dtype or \
+            (m > 1 and out2.stride(0) < n):
+        raise ValueError(f"out must be a [{m}, {n}] {x.dtype} tensor with unit column stride")
     if m == 0:
-        return out.reshape(*x.shape[:-1], n)
+        return out.reshape(*x.shape[:-1], n) if out.is_contiguous() else out
     nbytes = lib().dz_sbmm_workspace_bytes(m, n, k, int(segments.sorted))
     ws = _workspace(x.device, nbytes)
     args = SbmmArgs(
@@ -213,12 +223,14 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
         scales=scales_stacked.data_ptr(),
         qweight_stride=qweight_stacked.stride(0) * 4, meta_stride=meta_stacked.stride(0) * 2,
         scales_stride=scales_stacked.stride(0) * 2,
-        segments=segments.buf.data_ptr(), y=out.data_ptr(),
+        segments=segments.buf.data_ptr(), y=out2.data_ptr(),
         M=m, N=n, K=k, num_slots=qweight_stacked.shape[0], bits=bits, dtype=_dtype_code(x),
         tokens_sorted=int(segments.sorted),
-        workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+        flags=_lib.DZ_SBMM_ACCUMULATE if accumulate else 0,
+        workspace=ws.data_ptr(), workspace_bytes=ws.numel(),
+        y_stride=max(out2.stride(0), n))
     check(getattr(lib(), _entry)(ctypes.byref(args), _stream()), _entry)
-    return out.reshape(*x.shape[:-1], n)
+    return out.reshape(*x.shape[:-1], n) if out.is_contiguous() else out
 
 
 def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
@@ -245,36 +257,42 @@ def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
 _segment_cache = {}
 
 
+def _segments_for(indices: torch.Tensor, num_slots: int, device) -> Segments:
+    """Segment table of `indices`, rebuilt only when the tensor changed: the key is the
+    buffer's address and torch's version counter, which every in-place write through torch
+    (the `copy_` of the reference's _set_delta_mapping, serving/vllm/delta/models.py:407-430)
+    advances.  The cache keeps the tensor alive, so the address cannot be handed to another
+    tensor while the entry exists.  All layers of a step therefore share one build, with no
+    host synchronisation: whether the batch is sorted is left to the device (x is gathered
+    through the table's permutation, which is the identity for a sorted batch)."""
+    indices = indices.reshape(-1)
+    m = indices.numel()
+    key = (device.index, _stream(), num_slots)
+    stamp = (indices.data_ptr(), indices._version, m, indices.dtype)
+    ent = _segment_cache.get(key)
+    if ent is None or ent[0].max_tokens < m:
+        ent = [Segments(max(m, 256), num_slots, device), None, None]
+        _segment_cache[key] = ent
+    if ent[1] != stamp:
+        ent[0].build(indices)
+        ent[1] = stamp
+        ent[2] = indices
+    return ent[0]
+
+
 def apply_delta(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
                 meta_stacked: torch.Tensor, indices: torch.Tensor,
                 base_weight: torch.Tensor) -> torch.Tensor:
-    """Drop-in for the reference op: builds the segment table from `indices`
-    on every call.  Layers that share one mapping per step should build a
-    `Segments` once (set_mapping does) and call `sbmm`."""
-    m = indices.numel()
-    num_slots = qweight_stacked.shape[0]
-    key = (x.device.index, _stream(), num_slots)
-    seg = _segment_cache.get(key)
-    if seg is None or seg.max_tokens < m:
-        seg = Segments(max(m, 256), num_slots, x.device)
-        _segment_cache[key] = seg
-    seg.build(indices)
+    """Drop-in for the reference op (serving/vllm/delta/deltazip_marlin.py:10-19).  Enqueues
+    device work only: no host synchronisation and no allocation besides the result, so it can
+    sit inside a captured decode step as the reference's op does."""
+    seg = _segments_for(indices, qweight_stacked.shape[0], x.device)
     return sbmm(x, qweight_stacked, scales_stacked, meta_stacked, seg, base_weight)
 
 
 # ---------------------------------------------------------------------------
 # the "separate base output" form of the op: y += x dequant(delta)^T in place
 # ---------------------------------------------------------------------------
-
-def _segments_for(indices: torch.Tensor, num_slots: int, device) -> Segments:
-    m = indices.numel()
-    key = (device.index, _stream(), num_slots)
-    seg = _segment_cache.get(key)
-    if seg is None or seg.max_tokens < m:
-        seg = Segments(max(m, 256), num_slots, device)
-        _segment_cache[key] = seg
-    return seg.build(indices)
-
 
 def add_delta(y: torch.Tensor, x: torch.Tensor, qweight: torch.Tensor,
               qzeros: Optional[torch.Tensor], scales: torch.Tensor,
@@ -284,14 +302,13 @@ def add_delta(y: torch.Tensor, x: torch.Tensor, qweight: torch.Tensor,
     reference's add_delta (serving/vllm/delta/deltazip.py:14-38) on slot-layout stacks
     (`qweight`, `scales`, `meta` as `alloc_slots` makes them; the symmetric zero point and the
     single quantisation group are implicit, so `qzeros` and `g_idx` are accepted and ignored).
-    The delta products come from the SBMM kernel without its base half; the addition to the
-    caller's base output is one elementwise pass over [M, N]."""
+    One launch of the SBMM kernel without its base half, adding into y in its epilogue."""
     if meta is None:
         raise ValueError("slot-layout stacks need their 2:4 metadata (meta)")
     x2 = x.reshape(-1, x.shape[-1])
     y2 = y.view(-1, y.shape[-1])
-    seg = _segments_for(indices.reshape(-1), qweight.shape[0], x.device)
-    y2 += sbmm(x2, qweight, scales, meta, seg, None)
+    seg = _segments_for(indices, qweight.shape[0], x.device)
+    sbmm(x2, qweight, scales, meta, seg, None, out=y2, accumulate=True)
     return y
 
 
@@ -301,16 +318,18 @@ def add_delta_slice(y: torch.Tensor, x: torch.Tensor, qweight: torch.Tensor,
                     y_offset: int, y_slice_size: int, *, buffer: Optional[torch.Tensor] = None,
                     meta: Optional[torch.Tensor] = None) -> torch.Tensor:
     """add_delta into the columns [y_offset, y_offset + y_slice_size) of y
-    (serving/vllm/delta/deltazip.py:41-78; `scale` and `buffer` are unused there too)."""
+    (serving/vllm/delta/deltazip.py:41-78; `scale` and `buffer` are unused there too).  The
+    kernel writes the slice in place through its row stride; `y_offset` must be a multiple
+    of 8 elements."""
     if meta is None:
         raise ValueError("slot-layout stacks need their 2:4 metadata (meta)")
     x2 = x.reshape(-1, x.shape[-1])
     y2 = y.view(-1, y.shape[-1])
-    seg = _segments_for(indices.reshape(-1), qweight.shape[0], x.device)
-    part = sbmm(x2, qweight, scales, meta, seg, None)
-    if part.shape[-1] != y_slice_size:
-        raise ValueError(f"slice of {y_slice_size} columns, delta stack has {part.shape[-1]}")
-    y2[:, y_offset:y_offset + y_slice_size] += part
+    if scales.shape[-1] != y_slice_size:
+        raise ValueError(f"slice of {y_slice_size} columns, delta stack has {scales.shape[-1]}")
+    seg = _segments_for(indices, qweight.shape[0], x.device)
+    sbmm(x2, qweight, scales, meta, seg, None, out=y2[:, y_offset:y_offset + y_slice_size],
+         accumulate=True)
     return y
 
 
@@ -379,3 +398,94 @@ def apply_delta_uncompressed(x: torch.Tensor, delta_weights: torch.Tensor, indic
         w = base_embedding if d < 0 else delta_weights[d]
         out[rows] = base_gemm(x2[rows].contiguous(), w.contiguous())
     return out.reshape(*x.shape[:-1], n)
+
+
+# ---------------------------------------------------------------------------
+# the steps between the SBMM calls of a decoder layer (decode time)
+# ---------------------------------------------------------------------------
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+             residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = rmsnorm(x) * weight; with `residual`, first residual += x (in place) and the norm is
+    taken of the sum -- the reference's RMSNorm.forward with and without residual
+    (serving/vllm/model_executor/layers/layernorm.py:47-66)."""
+    _need_cuda(x, weight, residual)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty_like(x2)
+    if residual is not None and not residual.is_contiguous():
+        raise ValueError("residual must be contiguous (it is updated in place)")
+    check(lib().dz_rms_norm(x2.data_ptr(), residual.data_ptr() if residual is not None else None,
+                            weight.data_ptr(), out.data_ptr(), x2.shape[0], x2.shape[1], float(eps),
+                            _dtype_code(x), _stream()), "dz_rms_norm")
+    return out.reshape(x.shape)
+
+
+def silu_and_mul(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x[..., :I]) * x[..., I:] (serving/vllm/model_executor/layers/activation.py:17-40)."""
+    _need_cuda(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    inter = x2.shape[1] // 2
+    if out is None:
+        out = torch.empty((x2.shape[0], inter), dtype=x.dtype, device=x.device)
+    check(lib().dz_silu_and_mul(x2.data_ptr(), out.data_ptr(), x2.shape[0], inter, _dtype_code(x),
+                                _stream()), "dz_silu_and_mul")
+    return out.reshape(*x.shape[:-1], inter)
+
+
+def rotary_and_cache(qkv: torch.Tensor, positions: torch.Tensor, q_heads: int, kv_heads: int,
+                     rope_theta: float, k_cache: Optional[torch.Tensor] = None,
+                     v_cache: Optional[torch.Tensor] = None,
+                     slot_mapping: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotary embedding in place on the q and k heads of fused qkv rows [M, (q+2kv)*128] and, when
+    a cache is given, the write of k / v to cache slot `slot_mapping[token]`."""
+    _need_cuda(qkv, positions, k_cache, v_cache, slot_mapping)
+    if not qkv.is_contiguous() or positions.dtype != torch.int64:
+        raise ValueError("qkv must be contiguous and positions int64")
+    m = qkv.numel() // qkv.shape[-1]
+    if slot_mapping is not None and slot_mapping.dtype != torch.int64:
+        raise ValueError("slot_mapping must be int64")
+    check(lib().dz_rotary_and_cache(
+        qkv.data_ptr(), positions.data_ptr(),
+        slot_mapping.data_ptr() if slot_mapping is not None else None,
+        k_cache.data_ptr() if k_cache is not None else None,
+        v_cache.data_ptr() if v_cache is not None else None,
+        m, q_heads, kv_heads, qkv.shape[-1] // (q_heads + 2 * kv_heads), float(rope_theta),
+        _dtype_code(qkv), _stream()), "dz_rotary_and_cache")
+    return qkv
+
+
+_attn_ws = {}
+
+
+def paged_attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                           block_tables: torch.Tensor, seq_lens: torch.Tensor, q_heads: int,
+                           kv_heads: int, block_size: int, scale: float, splits: int = 1,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query token per sequence (the q part of fused qkv rows [B, (q+2kv)*128]) against the
+    paged cache; returns [B, q_heads*128]."""
+    _need_cuda(qkv, k_cache, v_cache, block_tables, seq_lens)
+    b = qkv.shape[0]
+    if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32 or not block_tables.is_contiguous():
+        raise ValueError("block_tables / seq_lens must be contiguous int32")
+    if out is None:
+        out = torch.empty((b, q_heads * 128), dtype=qkv.dtype, device=qkv.device)
+    ws_ptr, ws_bytes = None, 0
+    if splits > 1:
+        need = lib().dz_paged_attention_workspace_bytes(b, q_heads, kv_heads, splits)
+        key = (qkv.device.index, _stream())
+        ws = _attn_ws.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.zeros(need, dtype=torch.uint8, device=qkv.device)
+            _attn_ws[key] = ws
+        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+    check(lib().dz_paged_attention_decode(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_tables.data_ptr(), block_tables.shape[1], seq_lens.data_ptr(), b, q_heads, kv_heads,
+        128, block_size, float(scale), splits, ws_ptr, ws_bytes, _dtype_code(qkv), _stream()),
+        "dz_paged_attention_decode")
+    return out

@@ -75,9 +75,16 @@ def tensor_model_parallel_all_gather(x: torch.Tensor, dim: int = -1) -> torch.Te
     return torch.cat(parts, dim=dim)
 
 
+# Tensor-parallel cuts are made at whole 128-wide units on both sides of a column-parallel /
+# row-parallel pair (128 output rows of qkv / gate / up = 128 input columns of o_proj /
+# down_proj), so that a producer's shard is exactly its consumer's K range for every rank
+# count, also when the unit count does not divide evenly (Llama-2-7B: 11008 = 86 units).
+SHARD_UNIT = 128
+
+
 def shard_range(total: int, unit: int, rank: int, size: int):
-    """[lo, hi) of `total` for `rank`, cut at multiples of `unit` (whole 128-row tiles for
-    column-parallel layers, whole 64-column blocks for row-parallel ones)."""
+    """[lo, hi) of `total` for `rank`, cut at multiples of `unit` (use SHARD_UNIT for model
+    dimensions)."""
     if total % unit:
         raise ValueError(f"{total} is not a multiple of {unit}")
     units = total // unit

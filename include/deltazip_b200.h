@@ -127,16 +127,31 @@ typedef struct {
   int32_t tokens_sorted;    /* 1: caller guarantees `indices` were non-decreasing
                                (the reference's scheduler sorts each batch by
                                delta id, serving/vllm/core/scheduler.py:101-104);
-                               x is then read in place.  0: x is first gathered
-                               into sorted order inside the workspace.  A wrong
-                               promise is detected (DZ_ERR_INVALID_ARG in the
-                               workspace status word) and nothing is computed.  */
-  int32_t reserved;
+                               x is then read in place.  0: no promise -- x is
+                               first gathered into sorted order inside the
+                               workspace (a plain copy when the batch happens to
+                               be sorted); no host synchronisation either way.
+                               A wrong promise is detected (DZ_ERR_INVALID_ARG in
+                               the workspace status word) and nothing is computed. */
+  int32_t flags;            /* DZ_SBMM_* bits, 0 = none                          */
   void* workspace;          /* >= dz_sbmm_workspace_bytes(M, N, K, tokens_sorted);
                                zero-filled once by the caller before first use;
                                its first int is a status word (dz_read_status)  */
   size_t workspace_bytes;
+  int64_t y_stride;         /* elements between consecutive rows of y; 0 = N.
+                               With a stride > N the call writes the columns
+                               [0, N) of a wider output, i.e. one slice of a
+                               merged layer (add_delta_slice,
+                               serving/vllm/delta/deltazip.py:41-78)             */
 } dz_sbmm_args;
+
+/* flags of dz_sbmm_args */
+enum {
+  DZ_SBMM_ACCUMULATE = 1    /* y += result instead of y = result: the in-place form
+                               of the reference's GPTQ-layout ops (add_delta,
+                               serving/vllm/delta/deltazip.py:14-38); the sum is
+                               formed in fp32 and rounded once                    */
+};
 
 size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted);
 int dz_sbmm(const dz_sbmm_args* args, void* stream);
@@ -144,17 +159,26 @@ int dz_sbmm(const dz_sbmm_args* args, void* stream);
 /*
  * dz_sbmm for callers that cannot allocate device memory (no counterpart in the
  * reference, which allocates freely through PyTorch).  Same arguments and
- * results as dz_sbmm, but `workspace` / `workspace_bytes` are ignored: the
- * scratch lives in a fixed array inside the library, so the call makes no
- * cudaMalloc / cudaFree and calls no allocating routine.  Limits: M <=
- * dz_sbmm_static_max_tokens() (64) and tokens_sorted must be 1, otherwise
- * DZ_ERR_TOO_LARGE.  Each GPU that loads the library holds about 10.5 MB for
- * this array until the process exits.  The first call on a device looks up the
- * array's device address (make it before any stream capture).  All calls on a
- * device share the array: calls that overlap on the GPU race -- order them.
+ * results as dz_sbmm (w_base may be NULL, flags and y_stride are honoured), but
+ * `workspace` / `workspace_bytes` are ignored: the scratch lives in a fixed
+ * array inside the library, so the call makes no cudaMalloc / cudaFree and
+ * calls no allocating routine.  Limits: M <= dz_sbmm_static_max_tokens() (64)
+ * and tokens_sorted must be 1, otherwise DZ_ERR_TOO_LARGE.  Each GPU that loads
+ * the library holds about 10.5 MB for this array until the process exits.  The
+ * first call on a device looks up the array's device address (make it before
+ * any stream capture).  All calls on a device share the array: calls that
+ * overlap on the GPU race -- order them.
+ *
+ * Device-side findings (DZ_ERR_INVALID_ARG: a wrong tokens_sorted promise or a
+ * segment table built for another M / num_slots, in which case the kernel
+ * computes nothing and y is left as it was; DZ_ERR_TIMEOUT: a bounded wait ran
+ * out) land in a status word inside the array.  It stays set until
+ * dz_sbmm_static_status reads and clears it (synchronises `stream`; allocates
+ * nothing either).
  */
 int dz_sbmm_static(const dz_sbmm_args* args, void* stream);
 int dz_sbmm_static_max_tokens(void);
+int dz_sbmm_static_status(void* stream, int* host_out);
 
 /* Base GEMM alone, y = x W^T (all tokens -1); same argument block, the slot
  * pointers and `segments` may be NULL.
@@ -172,6 +196,42 @@ int dz_delta_embedding(const int64_t* token_ids, const void* indices, int index_
                        int hidden, const void* base_table, const void* delta_tables,
                        int64_t table_stride_bytes, int num_slots, int64_t vocab, void* y,
                        int* status_word, void* stream);
+
+/*
+ * The steps between the SBMM calls of a decoder layer at decode time, so that a decode step is a
+ * chain of this library's launches.  2-byte elements of `dtype`; 16-byte aligned pointers; all
+ * enqueue one kernel on `stream` and return.
+ *
+ * dz_rms_norm: residual == NULL: out = rmsnorm(x) * weight.  residual != NULL: residual = x +
+ *   residual, out = rmsnorm(residual) * weight (out may alias x).  x, out, residual [M, hidden],
+ *   hidden % 8 == 0, hidden <= 16384.  serving/csrc/ops.h:37-47 (rms_norm, fused_add_rms_norm),
+ *   semantics of serving/vllm/model_executor/layers/layernorm.py:27-66.
+ * dz_silu_and_mul: out[m, i] = silu(x[m, i]) * x[m, inter + i]; x [M, 2*inter], out [M, inter].
+ *   serving/csrc/ops.h:67.
+ * dz_rotary_and_cache: rotary position embedding (neox pairing, base `rope_theta`) in place on
+ *   the q and k heads of the fused rows qkv [M, (q_heads + 2*kv_heads) * 128], then k (rotated)
+ *   and v written to the paged cache at slot_mapping[token] = block * block_size + offset
+ *   (negative or slot_mapping == NULL: not cached).  Cache layout: [slots, kv_heads, 128] for K
+ *   and for V.  head_dim must be 128.  serving/csrc/ops.h:49 + serving/csrc/cache.h:18.
+ * dz_paged_attention_decode: one query token per sequence against its cached keys/values:
+ *   out [num_seqs, q_heads * 128]; q is read from the fused rows (q_row_stride elements apart);
+ *   block_tables int32 [num_seqs, max_blocks]; seq_lens int32 [num_seqs] (cached tokens,
+ *   the current one included).  splits > 1 divides every sequence's keys over that many CTAs
+ *   (for few long sequences) and needs `workspace` of dz_paged_attention_workspace_bytes(),
+ *   zero-filled once.  serving/csrc/ops.h:6 (paged_attention_v1).
+ */
+int dz_rms_norm(const void* x, void* residual, const void* weight, void* out, int M, int hidden,
+                float eps, int dtype, void* stream);
+int dz_silu_and_mul(const void* x, void* out, int M, int inter, int dtype, void* stream);
+int dz_rotary_and_cache(void* qkv, const int64_t* positions, const int64_t* slot_mapping,
+                        void* k_cache, void* v_cache, int M, int q_heads, int kv_heads,
+                        int head_dim, float rope_theta, int dtype, void* stream);
+size_t dz_paged_attention_workspace_bytes(int num_seqs, int q_heads, int kv_heads, int splits);
+int dz_paged_attention_decode(const void* qkv, int q_row_stride, void* out, const void* k_cache,
+                              const void* v_cache, const int32_t* block_tables, int max_blocks,
+                              const int32_t* seq_lens, int num_seqs, int q_heads, int kv_heads,
+                              int head_dim, int block_size, float scale, int splits,
+                              void* workspace, size_t workspace_bytes, int dtype, void* stream);
 
 /*
  * Delta swap-in: one asynchronous host->device copy of a delta's slot bytes

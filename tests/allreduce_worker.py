@@ -78,7 +78,7 @@ def main():
     x = torch.randn(m, k, generator=gen, device=dev).half()
     idx = torch.sort(torch.randint(-1, slots, (m,), generator=gen, device=dev))[0]
     full = ops.alloc_slots(slots, n, k, bits, dev)
-    lo, hi = parallel_state.shard_range(k, 64, rank, world)
+    lo, hi = parallel_state.shard_range(k, 128, rank, world)
     base = layers.RowParallelLinear(k, n, device=dev)
     base.weight.data.copy_(w[:, lo:hi])
     layer = layers.RowParallelLinearWithDelta(base)

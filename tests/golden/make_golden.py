@@ -75,6 +75,52 @@ def reference_case(quant, qlinear, n, k, bits, m, seed, zero_row=False):
     )
 
 
+def reference_checkpoint(quant, qlinear, out_dir, bits, seed, hidden=256, inter=512):
+    """A one-layer delta in the form the reference's compressor saves it
+    (deltazip/modeling/_base.py:597-648 for anything but the 4-bit structured-sparse re-pack,
+    which needs an external package): the QuantLinear buffers of every projection under
+    HuggingFace module names in deltazip-compressed.safetensors, plus compress_config.json with
+    the keys of deltazip/modeling/_base.py's config.  dense.npz holds what the reference's
+    unpack gives for each projection."""
+    import json
+    from safetensors.torch import save_file
+    g = torch.Generator().manual_seed(seed)
+    shapes = {"self_attn.q_proj": (hidden, hidden), "self_attn.k_proj": (hidden, hidden),
+              "self_attn.v_proj": (hidden, hidden), "self_attn.o_proj": (hidden, hidden),
+              "mlp.gate_proj": (inter, hidden), "mlp.up_proj": (inter, hidden),
+              "mlp.down_proj": (hidden, inter)}
+    state, dense = {}, {}
+    for name, (n, k) in shapes.items():
+        delta = torch.randn(n, k, generator=g, dtype=torch.float32) * 1e-3
+        quantizer = quant.Quantizer()
+        quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+        quantizer.find_params(delta, weight=True)
+        scale, zero = quantizer.scale.clone(), quantizer.zero.clone()
+        pruned = torch.zeros_like(delta, dtype=torch.bool)
+        for i in range(0, k, 4):
+            tmp = delta[:, i:i + 4] ** 2
+            pruned.scatter_(1, i + torch.topk(tmp, 2, dim=1, largest=False)[1], True)
+        q_in = delta.clone()
+        q_in[pruned] = 0
+        wq = quant.quantize(q_in, scale, zero, quantizer.maxq)
+        layer = qlinear.QuantLinear(bits, k, n, bias=False)
+        lin = torch.nn.Linear(k, n, bias=False)
+        lin.weight.data = wq.clone()
+        layer.pack(lin, scale.clone(), zero.clone(), g_idx=None)
+        for buf in ("qweight", "qzeros", "scales", "g_idx"):
+            state[f"model.layers.0.{name}.{buf}"] = getattr(layer, buf).clone().contiguous()
+        dense[name] = layer.unpack().weight.data.half().numpy()
+    state["model.norm.weight"] = torch.ones(hidden, dtype=torch.float16)       # an uncompressed module
+    os.makedirs(out_dir, exist_ok=True)
+    save_file(state, os.path.join(out_dir, "deltazip-compressed.safetensors"))
+    with open(os.path.join(out_dir, "compress_config.json"), "w") as fh:
+        json.dump({"bits": bits, "group_size": -1, "sparsity": 0.5, "damp_percent": 0.01,
+                   "desc_act": False, "sym": True, "true_sequential": True, "lossless": "none",
+                   "prunen": 2, "prunem": 4, "block_size": 128}, fh, indent=2)
+    np.savez_compressed(os.path.join(out_dir, "dense.npz"), **dense)
+    print(out_dir, {k: tuple(v.shape) for k, v in state.items() if k.endswith("qweight")})
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path of a deltazip checkout>")
@@ -95,6 +141,8 @@ def main():
         assert bool(out["dense_is_fp16_exact"])
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
         print(name, {kk: getattr(v, "shape", None) for kk, v in out.items()})
+    reference_checkpoint(quant, qlinear, os.path.join(HERE, "ref_ckpt_b4"), 4, seed=10)
+    reference_checkpoint(quant, qlinear, os.path.join(HERE, "ref_ckpt_b2"), 2, seed=11)
 
 
 if __name__ == "__main__":

@@ -16,7 +16,7 @@ def build(bits, seed=0):
     from deltazip_b200.config import DeltaConfig
     from deltazip_b200.llama import LlamaConfig, LlamaForCausalLM
     from deltazip_b200.models import DeltaModel, DeltaModelManager
-    cfg = LlamaConfig(hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=768, num_hidden_layers=2,
                       num_attention_heads=4, vocab_size=512)
     torch.manual_seed(seed)
     model = LlamaForCausalLM(cfg, seed=seed)

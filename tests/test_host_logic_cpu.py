@@ -103,7 +103,7 @@ def test_shard_gptq_tensors_matches_slices_of_the_dense_delta():
     from deltazip_b200.models import shard_gptq_tensors
     from deltazip_b200.parallel_state import shard_range
     rng = np.random.default_rng(5)
-    n, k = 384, 320
+    n, k = 384, 640
     for bits in (2, 4):
         delta = (rng.standard_normal((n, k)) * 1e-2).astype(np.float32)
         wq, scale, zero = orc.compress_delta(delta, bits)
@@ -119,6 +119,34 @@ def test_shard_gptq_tensors_matches_slices_of_the_dense_delta():
         for world in (2, 5):
             for rank in range(world):
                 rq, rz, rs = shard_gptq_tensors(qw, qz, sc, bits, "row", rank, world)
-                lo, hi = shard_range(k, 64, rank, world)
+                lo, hi = shard_range(k, 128, rank, world)
                 got = orc.unpack(rq.numpy(), rz.numpy(), rs.numpy(), bits)
                 assert got.shape == (n, hi - lo) and np.array_equal(got, dense[:, lo:hi])
+
+
+def test_tensor_parallel_cuts_pair_producer_and_consumer():
+    """For every rank count the shard a column-parallel layer produces is exactly the K range of
+    the row-parallel layer that consumes it (qkv -> o_proj over the attention width, gate/up ->
+    down_proj over the MLP width), also when the 128-wide unit count does not divide by the
+    rank count (Llama-2-7B: 11008 = 86 units)."""
+    from deltazip_b200.parallel_state import SHARD_UNIT
+    for hidden, inter in ((4096, 11008), (5120, 13824), (8192, 28672)):
+        for tp in (1, 2, 4, 8):
+            seen_h, seen_i = 0, 0
+            for rank in range(tp):
+                q = shard_range(hidden, SHARD_UNIT, rank, tp)        # q heads of this rank
+                o_k = shard_range(hidden, SHARD_UNIT, rank, tp)      # o_proj input columns
+                gate = shard_range(inter, SHARD_UNIT, rank, tp)
+                down_k = shard_range(inter, SHARD_UNIT, rank, tp)
+                assert q == o_k and gate == down_k
+                assert (q[1] - q[0]) % 128 == 0 and (gate[1] - gate[0]) % 128 == 0
+                assert q[0] == seen_h and gate[0] == seen_i
+                seen_h, seen_i = q[1], gate[1]
+            assert seen_h == hidden and seen_i == inter
+    # the benchmark's per-rank projection table uses the same cuts
+    import bench
+    for tp in (2, 4, 8):
+        for rank in range(tp):
+            pr = {name: (n, k) for name, n, k, _ in bench.projections(tp, rank)}
+            assert pr["qkv_proj"][0] == 3 * pr["o_proj"][1]
+            assert pr["gate_up_proj"][0] == 2 * pr["down_proj"][1]

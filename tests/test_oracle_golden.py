@@ -101,3 +101,27 @@ def test_torch_port_matches_golden(case):
     ref = (case["y_base"].astype(np.float32) + case["y_delta"].astype(np.float32))
     ref[0] = case["y_base"][0]
     assert O.rel_l2(y, ref) <= 3e-3
+
+
+def test_staged_reference_code_agrees_with_the_restatements():
+    """Where the reference's own files are staged (oracle/_ref, made by oracle/make_ref.py), its
+    QuantLinear.forward / unpack driven by oracle/reference_path.py give what the numpy and
+    torch restatements give on the same GPTQ tensors."""
+    import torch
+    from oracle import deltazip_oracle as orc
+    from oracle import reference_path as R
+    from oracle import torch_port as T
+    if not R.available():
+        pytest.skip("reference files not staged on this machine")
+    for bits in (2, 4):
+        w, deltas = orc.make_layer(256, 384, 3, bits, seed=bits)
+        x, idx = orc.make_tokens(21, 384, 3, seed=bits, base_frac=0.2)
+        layers = [R.quant_linear(torch.from_numpy(qw), torch.from_numpy(qz), torch.from_numpy(sc), b)
+                  for qw, qz, sc, b in deltas]
+        y = R.apply_delta(torch.from_numpy(x), torch.from_numpy(w), layers, torch.from_numpy(idx))
+        assert orc.rel_l2(y.numpy(), orc.apply_delta(x, w, deltas, idx)) <= 1e-3
+        tdeltas = [tuple(torch.from_numpy(t) for t in d[:3]) + (d[3],) for d in deltas]
+        y2 = T.apply_delta(torch.from_numpy(x), torch.from_numpy(w), tdeltas, torch.from_numpy(idx))
+        assert orc.rel_l2(y.numpy(), y2.numpy()) <= 1e-3
+        dense_t = R.unpack_dense_t(layers[0])
+        assert (dense_t.t().numpy().view(np.uint16) == orc.unpack(*deltas[0]).view(np.uint16)).all()
