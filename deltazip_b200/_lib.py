@@ -31,6 +31,7 @@ DZ_DTYPE_F32 = 2
 DZ_INDEX_I32 = 0
 DZ_INDEX_I64 = 1
 DZ_SBMM_ACCUMULATE = 1
+DZ_SBMM_INPUTS_STABLE = 2
 
 
 class SbmmArgs(Structure):
@@ -89,6 +90,7 @@ _SIGNATURES = {
                                           c_void_p, c_size_t, c_int, c_void_p]),
     "dz_slot_upload": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "dz_slot_reset": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "dz_stream_fence": (c_int, [c_void_p]),
     "dz_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
     "dz_allreduce_region_bytes": (c_size_t, [c_size_t]),
     "dz_allreduce_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_size_t]),

@@ -14,6 +14,16 @@ void set_last_cuda_error(cudaError_t e, const char* where) {
 
 int launch_sbmm_simt(const dz_sbmm_args& a, bool base_only, cudaStream_t st);
 
+// An empty kernel launched the ordinary way: it starts only after everything before it in the
+// stream has completed with its writes visible, so a later kernel that begins early under
+// programmatic dependent launch overlaps at most this kernel, never the writers before it.
+__global__ void stream_fence_kernel() {}
+int launch_stream_fence(cudaStream_t st) {
+  stream_fence_kernel<<<1, 32, 0, st>>>();
+  DZ_CUDA_OK(cudaGetLastError());
+  return DZ_OK;
+}
+
 static int check_shape(int N, int K, int bits) {
   if (N <= 0 || K <= 0) return DZ_ERR_INVALID_ARG;
   if (N % kTileN != 0 || K % kBlockK != 0) return DZ_ERR_SHAPE;
@@ -38,7 +48,7 @@ int check_sbmm_args(const dz_sbmm_args* a, bool base_only, bool check_workspace)
         (a->meta_stride & 15) || (a->scales_stride & 1))
       return DZ_ERR_ALIGNMENT;
   }
-  if (a->flags & ~(int32_t)DZ_SBMM_ACCUMULATE) return DZ_ERR_INVALID_ARG;
+  if (a->flags & ~(int32_t)(DZ_SBMM_ACCUMULATE | DZ_SBMM_INPUTS_STABLE)) return DZ_ERR_INVALID_ARG;
   if (a->y_stride != 0 && (a->y_stride < a->N || (a->y_stride & 7))) return DZ_ERR_INVALID_ARG;
   if (!check_workspace) return DZ_OK;
   if (a->workspace_bytes <
@@ -94,8 +104,9 @@ int dz_convert_from_gptq(const int32_t* qweight, const int32_t* qzeros, const ui
   int rc = check_shape(N, K, bits);
   if (rc) return rc;
   if (!aligned16(slot_qweight) || !aligned16(slot_meta)) return DZ_ERR_ALIGNMENT;
-  return launch_convert_from_gptq(qweight, qzeros, scales, N, K, bits, slot_qweight, slot_meta,
-                                  slot_scales, status_word, (cudaStream_t)stream);
+  rc = launch_convert_from_gptq(qweight, qzeros, scales, N, K, bits, slot_qweight, slot_meta,
+                                slot_scales, status_word, (cudaStream_t)stream);
+  return rc ? rc : launch_stream_fence((cudaStream_t)stream);
 }
 
 int dz_unpack(const void* slot_qweight, const void* slot_meta, const uint16_t* slot_scales, int N,
@@ -120,7 +131,8 @@ int dz_build_segments(const void* indices, int index_dtype, int M, int num_slots
   if (M < 0 || num_slots < 0 || num_slots > kMaxSlots) return DZ_ERR_INVALID_ARG;
   if (index_dtype != DZ_INDEX_I32 && index_dtype != DZ_INDEX_I64) return DZ_ERR_INVALID_ARG;
   if (!aligned16(segments)) return DZ_ERR_ALIGNMENT;
-  return launch_build_segments(indices, index_dtype, M, num_slots, segments, (cudaStream_t)stream);
+  int rc = launch_build_segments(indices, index_dtype, M, num_slots, segments, (cudaStream_t)stream);
+  return rc ? rc : launch_stream_fence((cudaStream_t)stream);
 }
 
 size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted) {
@@ -144,7 +156,7 @@ int dz_sbmm_simt(const dz_sbmm_args* args, void* stream) {
   int rc = check_sbmm_args(args, false, true);
   if (rc || args->M == 0) return rc;
   if (args->dtype != DZ_DTYPE_F16) return DZ_ERR_UNSUPPORTED;   // the twin is fp16 only
-  if (args->flags || (args->y_stride && args->y_stride != args->N) || !args->w_base)
+  if ((args->flags & DZ_SBMM_ACCUMULATE) || (args->y_stride && args->y_stride != args->N) || !args->w_base)
     return DZ_ERR_UNSUPPORTED;                                   // plain y = base + delta only
   return launch_sbmm_simt(*args, false, (cudaStream_t)stream);
 }
@@ -161,9 +173,14 @@ int dz_slot_upload(void* dst_device, const void* src_pinned_host, size_t bytes, 
 
 int dz_slot_reset(void* dst_device, size_t bytes, void* stream) {
   if (!dst_device) return DZ_ERR_INVALID_ARG;
-  if (bytes) DZ_CUDA_OK(cudaMemsetAsync(dst_device, 0, bytes, (cudaStream_t)stream));
+  if (bytes) {
+    DZ_CUDA_OK(cudaMemsetAsync(dst_device, 0, bytes, (cudaStream_t)stream));
+    return launch_stream_fence((cudaStream_t)stream);
+  }
   return DZ_OK;
 }
+
+int dz_stream_fence(void* stream) { return launch_stream_fence((cudaStream_t)stream); }
 
 int dz_read_status(int* status_word, void* stream, int* host_out) {
   if (!status_word || !host_out) return DZ_ERR_INVALID_ARG;

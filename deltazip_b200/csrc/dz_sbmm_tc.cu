@@ -44,6 +44,7 @@
 // from phase n + 2).
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -57,16 +58,45 @@ constexpr int kNumWG = 4;                      // warpgroups (128 threads each)
 constexpr int kWarpWX = 0;                     // TMA producer: W tiles, x half-tiles
 constexpr int kWarpBase = 1;                   // base MMA issuer, TMEM owner
 constexpr int kWarpR = 2;                      // bulk-copy producer: packed delta stages
-constexpr int kWarpIssuer0 = 3;                // delta MMA issuers: warps 3..6
-constexpr int kFirstWGWarp = 7;                 // any 4 consecutive warps cover the 4 TMEM lane quarters
+// Role layout (overridable at compile time for experiments):
+//   DZ_ISSUER_WARPS  delta MMA issuer warps (one issuing thread each) starting at warp 3; with
+//                    2 * classes <= DZ_ISSUER_WARPS every class has two issuers
+//   DZ_FIRST_WG_WARP first of the 16 expansion / epilogue warps
+//   DZ_SVC_REGS / DZ_EXP_REGS  when non-zero the service warps (below DZ_FIRST_WG_WARP, which must
+//                    then be a multiple of 4) shrink to DZ_SVC_REGS registers per thread and the
+//                    expansion warps grow to DZ_EXP_REGS (setmaxnreg)
+#ifndef DZ_ISSUER_WARPS
+#define DZ_ISSUER_WARPS 4
+#endif
+#ifndef DZ_FIRST_WG_WARP
+#define DZ_FIRST_WG_WARP (3 + DZ_ISSUER_WARPS)
+#endif
+#ifndef DZ_SVC_REGS
+#define DZ_SVC_REGS 0
+#define DZ_EXP_REGS 0
+#endif
+constexpr int kWarpIssuer0 = 3;
+constexpr int kIssuerWarps = DZ_ISSUER_WARPS;
+constexpr int kFirstWGWarp = DZ_FIRST_WG_WARP;   // any 4 consecutive warps cover the 4 TMEM lane quarters
+constexpr int kServiceRegs = DZ_SVC_REGS, kExpandRegs = DZ_EXP_REGS;
+static_assert(kWarpIssuer0 + kIssuerWarps <= kFirstWGWarp, "role layout");
+static_assert(kServiceRegs == 0 || kFirstWGWarp % 4 == 0, "setmaxnreg works on whole warpgroups");
+static_assert((kFirstWGWarp * kServiceRegs + 4 * kNumWG * kExpandRegs) * 32 <= 65536, "register file");
 constexpr int kThreads = 32 * kFirstWGWarp + 128 * kNumWG;
 constexpr int kUnitK = 128;                    // dense k per work unit
 constexpr int kWTile = 128 * 128;              // bytes: 128 rows x 128 B
-constexpr int kRawBytes = 4096;                // codes of one unit (4-bit)
 constexpr int kMetaBytes = 2048;               // metadata of one unit
-constexpr int kRStage = kRawBytes + kMetaBytes;
+// codes of one unit: 128 rows x 64 kept values x bits; a packed stage = codes, then metadata
+__host__ __device__ constexpr int raw_bytes(int bits) { return 128 * 64 * bits / 8; }
+__host__ __device__ constexpr int rstage_bytes(int bits) { return raw_bytes(bits) + kMetaBytes; }
+#ifndef DZ_MAX_R_PER_CLASS
+#define DZ_MAX_R_PER_CLASS 6
+#endif
+#ifndef DZ_W_STAGES_WIDE
+#define DZ_W_STAGES_WIDE 3      // W ring depth for token blocks wider than 64 columns
+#endif
 constexpr int kWinBytes = 2 * kMaxWindowCols * 128;   // window buffer (B operand of one stage)
-constexpr int kMaxW = 4, kMaxX = 4, kMaxR = 16, kMaxBuf = 8;
+constexpr int kMaxW = 4, kMaxX = 4, kMaxR = 24, kMaxBuf = 8;
 constexpr int kMaxWin = 128;                   // windows of one token block
 constexpr int kTmemCols = 512;
 constexpr unsigned long long kTimeoutNs = 400ull * 1000 * 1000;
@@ -92,6 +122,7 @@ struct Params {
   int token_block, row0, cols;     // this launch: sorted rows [row0, row0 + cols)
   int base_only, delta_only, tokens_sorted;   // delta_only: no base product (w_base absent)
   int accumulate;                             // y += result
+  int stable;                                 // weights, slots and table are not the predecessor's output
   long long ldy;                              // elements between rows of y
   int grid, total_units, epi_units;   // total_units counts virtual units
   int w_stages, x_stages, r_per_class, xb_bytes;
@@ -459,6 +490,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.counters) + 4096) +
       (size_t)blockIdx.x * 8;
   if (INSTR && threadIdx.x == 0) tl[0] = globaltimer();
+  // INSTR: cycles spent by expansion warpgroup 0 (thread 0) and by the class-0 issuer in each
+  // part of their loops, 16 x u64 per CTA behind the parking slots of the last grid CTA
+  unsigned long long* const acct =
+      reinterpret_cast<unsigned long long*>(p.partials + (size_t)kMaxCtas * 2 * p.cols * 128 - 160 * 16 * 2) +
+      (size_t)blockIdx.x * 16;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -549,15 +585,25 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile int* abort_flag = &s_abort;
 
   // Programmatic dependent launch: this grid may be scheduled while its predecessor in the
-  // stream is still draining.  Nothing the predecessor writes (x, the segment table, the
-  // shared workspace) is touched before this wait, which returns once the predecessor has
-  // completed and its writes are visible; then the next kernel in the stream is allowed to be
-  // scheduled early in turn.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // stream is still draining.  Nothing the predecessor may write is touched before the wait,
+  // which returns once the predecessor has completed and its writes are visible; then the next
+  // kernel in the stream is allowed to be scheduled early in turn.
+  //   default: the predecessor may have written anything (x, the segment table, weights), so
+  //            every thread waits here;
+  //   stable : the caller states that the base weight, the slot stacks and the segment table are
+  //            not the predecessor's output.  Only x (and the shared workspace, y) still depend
+  //            on it, and they are first touched by copies the TMA producer thread issues, so
+  //            that thread alone waits (at the start of its role) and everything else -- the
+  //            table, the first W tiles, the packed stages, the expansion of the first windows
+  //            -- proceeds under the predecessor's tail.
+  if (!p.stable) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   if (INSTR && threadIdx.x == 0) tl[1] = globaltimer();
 
-  // The first x and W tiles are requested at once; the producer warp skips them later.
+  // The first W tiles (and, once the wait is behind, the first x tiles) are requested at once;
+  // the producer warp skips them later.
   if (threadIdx.x == 0) {
     int issued = 0;
     const int npre = min(p.w_stages, p.x_stages);
@@ -565,9 +611,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
       const int nhalf = min(2, (p.K - k0) / kBlockK);
       for (int h = 0; h < nhalf && issued < npre; ++h, ++issued) {
-        const uint32_t xfull = smem_u32(&bar_x_full[issued]);
-        mbar_expect_tx(xfull, p.xb_bytes);
-        tma_load_2d(s_xring + issued * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
+        if (!p.stable) {
+          const uint32_t xfull = smem_u32(&bar_x_full[issued]);
+          mbar_expect_tx(xfull, p.xb_bytes);
+          tma_load_2d(s_xring + issued * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
+        }
         if (!p.delta_only) {
           const uint32_t wfull = smem_u32(&bar_w_full[issued]);
           mbar_expect_tx(wfull, kWTile);
@@ -634,7 +682,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // active expansion warpgroup
     for (int i = 0; i < kMaxX; ++i)
       mbar_init(smem_u32(&bar_x_empty[i]), 1 + (nwin > 0 ? 128 * C : 0));
-    mbar_init(smem_u32(bar_acc_full), 1 + (nwin > 0 ? C : 0));
+    mbar_init(smem_u32(bar_acc_full), 1 + (nwin > 0 ? (2 * C <= kIssuerWarps ? 2 * C : C) : 0));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (bad && blockIdx.x == 0) atomicCAS(p.status, 0, (int)DZ_ERR_INVALID_ARG);
   }
@@ -650,23 +698,34 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
 
   if (INSTR && threadIdx.x == 0) tl[2] = globaltimer();
-  const int npre = s_npre;
+  // register hand-over between the role groups (whole warpgroups execute the same form)
+  if (kServiceRegs != 0) {
+    if (warp < kFirstWGWarp) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs));
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kExpandRegs));
+  }
+  const int npre_w = s_npre;                     // W half-tiles requested in the prologue
+  const int npre_x = p.stable ? 0 : s_npre;      // x half-tiles requested in the prologue
   const uint32_t a_col0 = 2 * p.dcols;          // TMEM column of expanded-A buffer 0
   const uint32_t e_col0 = a_col0 + nbuf * 32;   // TMEM column of metadata buffer 0
 
   if (bad) {
     // rejected batch: nothing runs, but the tiles requested in the prologue must land before
     // this CTA's shared memory is released
-    if (threadIdx.x == 0)
-      for (int i = 0; i < npre; ++i) {
-        mbar_wait(smem_u32(&bar_x_full[i]), 0, abort_flag, nullptr);
-        if (!p.delta_only) mbar_wait(smem_u32(&bar_w_full[i]), 0, abort_flag, nullptr);
-      }
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < npre_x; ++i) mbar_wait(smem_u32(&bar_x_full[i]), 0, abort_flag, nullptr);
+      if (!p.delta_only)
+        for (int i = 0; i < npre_w; ++i) mbar_wait(smem_u32(&bar_w_full[i]), 0, abort_flag, nullptr);
+    }
   } else if (warp == kWarpWX) {
     // ====================== TMA producer: W tiles and x half-tiles ======================
     if (lane == 0) {
+      if (p.stable) {
+        // the only thread whose copies read the predecessor's output
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      }
       Ring rw(p.w_stages, 1), rx(p.x_stages, 1);
-      int cnt = 0;   // half-tiles so far; the first `npre` were requested in the prologue
+      int cnt = 0;   // half-tiles so far; the first ones were requested in the prologue
       for (int u = u_begin; u < u_end;) {
         const int tile = u / KU, ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
@@ -675,17 +734,17 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const int k0 = ku * kUnitK;
           const int nhalf = min(2, (p.K - k0) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
-            if (cnt >= npre) {
+            if (cnt >= npre_x) {
               mbar_wait(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status);
               const uint32_t xfull = smem_u32(&bar_x_full[rx.idx]);
               mbar_expect_tx(xfull, p.xb_bytes);
               tma_load_2d(s_xring + rx.idx * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
-              if (!p.delta_only) {
-                mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
-                const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
-                mbar_expect_tx(wfull, kWTile);
-                tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
-              }
+            }
+            if (!p.delta_only && cnt >= npre_w) {
+              mbar_wait(smem_u32(&bar_w_empty[rw.idx]), rw.par, abort_flag, p.status);
+              const uint32_t wfull = smem_u32(&bar_w_full[rw.idx]);
+              mbar_expect_tx(wfull, kWTile);
+              tma_load_2d(s_wring + rw.idx * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
             }
             ++cnt;
             rx.advance();
@@ -722,10 +781,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               mbar_wait(smem_u32(&bar_r_empty[slot_idx]), par, abort_flag, p.status);
               const uint32_t full = smem_u32(&bar_r_full[slot_idx]);
               mbar_expect_tx(full, code_bytes + meta_bytes);
-              const uint32_t dst = s_rring + slot_idx * kRStage;
+              const uint32_t dst = s_rring + slot_idx * rstage_bytes(BITS);
               bulk_load(dst, p.qweight + (size_t)slot * p.qstride + blk * codes_block_bytes(BITS),
                         code_bytes, full);
-              bulk_load(dst + kRawBytes,
+              bulk_load(dst + raw_bytes(BITS),
                         p.meta + (size_t)slot * p.mstride + blk * kMetaBlockBytes, meta_bytes, full);
               if (++rs == p.r_per_class) { rs = 0; par ^= 1; }
             }
@@ -770,24 +829,38 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       if (INSTR) tl[4] = globaltimer();
     }
-  } else if (warp >= kWarpIssuer0 && warp < kWarpIssuer0 + 4) {
-    // =========================== delta MMA issuer of class t ===========================
-    const int t = warp - kWarpIssuer0;
-    if (lane == 0 && t < C && nwin > 0) {
+  } else if (warp >= kWarpIssuer0 && warp < kWarpIssuer0 + kIssuerWarps) {
+    // =========================== delta MMA issuers of class t ===========================
+    // A thread's MMAs cost ~200 cycles each to issue whatever their width, and a window needs
+    // four.  Where the warps allow it (2 * classes <= kIssuerWarps) a class has two issuing
+    // threads: one takes the class's even windows (expanded-A buffer 0), the other the odd ones
+    // (buffer 1).  Different windows of a class put their non-zero products into different
+    // accumulator columns, so the order in which the two threads' MMAs run changes no sum.
+    const int iw = warp - kWarpIssuer0;
+    const bool paired = 2 * C <= kIssuerWarps;
+    const int t = iw % C;
+    const int par = paired ? iw / C : -1;      // -1: this thread takes every window of its class
+    if (lane == 0 && iw < (paired ? 2 * C : C) && nwin > 0) {
       const int cnt_t = (nwin - t + C - 1) / C;
       int pacc = 1, n = 0;
+      long long i_wait = 0, i_issue = 0, i_acc = 0, tq = 0;
       for (int u = u_begin; u < u_end;) {
         const int ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
+        if (INSTR) tq = clock64();
         mbar_wait(smem_u32(bar_acc_empty), pacc, abort_flag, p.status);
+        if (INSTR) i_acc += clock64() - tq;
         pacc ^= 1;
         tc_fence_after();
         for (int ku = ku0; ku < ku1; ++ku) {
           const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
           for (int j = 0; j < cnt_t; ++j, ++n) {
+            if (par >= 0 && (n & 1) != par) continue;
             const WinS ws = s_win[t + j * C];
             const int buf = t + C * (n & 1);
+            if (INSTR) tq = clock64();
             mbar_wait(smem_u32(&bar_a_ready[buf]), (n >> 1) & 1, abort_flag, p.status);
+            if (INSTR) { const long long t2 = clock64(); i_wait += t2 - tq; tq = t2; }
             tc_fence_after();
             const uint32_t win_lo = desc_lo(s_winbuf + buf * kWinBytes);
             const uint32_t idesc = make_idesc<DT>(ws.ncols, true);
@@ -797,11 +870,13 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             umma_ts_sp_x2(dcol, acol, win_lo, ecol, idesc);
             if (nhalf == 2) umma_ts_sp_x2(dcol, acol + 16, win_lo + ws.ncols * 8, ecol + 2, idesc);
             umma_commit(smem_u32(&bar_a_free[buf]));
+            if (INSTR) i_issue += clock64() - tq;
           }
         }
         umma_commit(smem_u32(bar_acc_full));
         u += ku1 - ku0;
       }
+      if (INSTR && iw == 0) { acct[8] = i_wait; acct[9] = i_issue; acct[10] = i_acc; acct[11] = n; }
     }
   } else if (warp >= kFirstWGWarp) {
     // ================= code expansion (class = warpgroup) + epilogue =================
@@ -817,6 +892,8 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int pacc = 0, n = 0, rs = 0;
     uint32_t rpar = 0;
     bool cta_first_fragment = true;
+    long long a_x = 0, a_r = 0, a_free = 0, a_exp = 0, a_win = 0, a_fin = 0, a_epi = 0, tq = 0;
+    const bool acc_on = INSTR && ep_tid == 0;
 
     for (int u = u_begin; u < u_end;) {
       const int tile = u / KU, ku0 = u % KU;
@@ -828,6 +905,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // the unit's x half-tiles
         uint32_t xsrc0 = 0, xsrc1 = 0;
         int xslot0 = 0, xslot1 = 0;
+        if (acc_on) tq = clock64();
         for (int h = 0; h < nhalf; ++h) {
           mbar_wait(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status);
           if (h == 0) { xsrc0 = s_xring + rx.idx * p.xb_bytes; xslot0 = rx.idx; }
@@ -838,11 +916,14 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const WinS ws = s_win[wg + j * C];
           const int buf = wg + C * (n & 1);
           const int rslot = wg * p.r_per_class + rs;
+          if (acc_on) { const long long t2 = clock64(); if (j == 0) a_x += t2 - tq; tq = t2; }
           mbar_wait(smem_u32(&bar_r_full[rslot]), rpar, abort_flag, p.status);
+          if (acc_on) { const long long t2 = clock64(); a_r += t2 - tq; tq = t2; }
           if (++rs == p.r_per_class) { rs = 0; rpar ^= 1; }
           mbar_wait(smem_u32(&bar_a_free[buf]), ((n >> 1) & 1) ^ 1, abort_flag, p.status);
+          if (acc_on) { const long long t2 = clock64(); a_free += t2 - tq; tq = t2; }
           tc_fence_after();
-          const uint32_t raw = s_rring + rslot * kRStage;
+          const uint32_t raw = s_rring + rslot * rstage_bytes(BITS);
           const uint32_t my_win = s_winbuf + buf * kWinBytes;
           uint32_t mw[4] = {0, 0, 0, 0};
           auto expand_half = [&](const int h) {
@@ -860,7 +941,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             // compressed A of this half: 32 fp16 = 16 columns of the row's lane
             tmem_st16(lane_addr + a_col0 + buf * 32 + h * 16, o);
-            const uint2 m2 = lds64(raw + kRawBytes + h * 1024 + r * 8);
+            const uint2 m2 = lds64(raw + raw_bytes(BITS) + h * 1024 + r * 8);
             mw[h * 2] = m2.x;
             mw[h * 2 + 1] = m2.y;
           };
@@ -869,6 +950,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tmem_st4(lane_addr + e_col0 + buf * 4, mw[0], mw[1], mw[2], mw[3]);
           // the packed stage has been consumed
           mbar_arrive(smem_u32(&bar_r_empty[rslot]));
+          if (acc_on) { const long long t2 = clock64(); a_exp += t2 - tq; tq = t2; }
           // the slot's token window: rows of the resident x half-tiles, other slots' rows zeroed
           // (16-byte chunk c of a half = row c >> 3; both halves' chunks are requested together)
           {
@@ -889,10 +971,12 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               if (nhalf == 2) sts128(my_win + half_bytes + c * 16, v1);
             }
           }
+          if (acc_on) { const long long t2 = clock64(); a_win += t2 - tq; tq = t2; }
           fence_proxy_async();
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_a_ready[buf]));
+          if (acc_on) { const long long t2 = clock64(); a_fin += t2 - tq; tq = t2; }
         }
         // this warpgroup no longer reads the unit's x half-tiles
         mbar_arrive(smem_u32(&bar_x_empty[xslot0]));
@@ -907,6 +991,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // epilogues and depend on nothing), then adds their partials to its own accumulators in
       // fragment order, straight from registers.  Every other fragment parks its partial and
       // leaves with a single fire-and-forget release increment.
+      if (acc_on) tq = clock64();
       const bool full_tile = (ku0 == 0 && ku1 == KU);
       int c_first = 0, nfrag = 1, ticket = 0;
       uint32_t slot_first = 0;   // parking slot (0/1) of the tile's first fragment
@@ -1111,8 +1196,13 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       cta_first_fragment = false;
       u += ku1 - ku0;
+      if (acc_on) a_epi += clock64() - tq;
     }
     if (INSTR && ep_tid == 0) tl[6] = globaltimer();
+    if (acc_on) {
+      acct[0] = a_x; acct[1] = a_r; acct[2] = a_free; acct[3] = a_exp; acct[4] = a_win;
+      acct[5] = a_fin; acct[6] = a_epi; acct[7] = n;
+    }
   }
 
   // ---- teardown ----
@@ -1268,11 +1358,19 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.base_only = base_only ? 1 : 0;
   p.delta_only = (!base_only && a.w_base == nullptr) ? 1 : 0;
   p.accumulate = (a.flags & DZ_SBMM_ACCUMULATE) ? 1 : 0;
+  p.stable = (a.flags & DZ_SBMM_INPUTS_STABLE) ? 1 : 0;
   p.ldy = a.y_stride ? a.y_stride : a.N;
   p.tokens_sorted = sorted ? 1 : 0;
   p.epi_units = kEpilogueUnits;
   p.total_units = p.num_tiles * (p.num_kunits + p.epi_units);
   p.grid = min(min(di.sms, kMaxCtas), p.num_tiles * p.num_kunits);
+#ifdef DZ_TUNE_ENV
+  {
+    static const int min_units = getenv("DZ_MIN_UNITS") ? atoi(getenv("DZ_MIN_UNITS")) : 0;
+    if (min_units > 0)
+      p.grid = max(min(p.grid, p.num_tiles), min(p.grid, p.num_tiles * (p.num_kunits + p.epi_units) / min_units));
+  }
+#endif
   if ((long long)(p.total_units + 1) * p.grid >= (1ll << 31)) return DZ_ERR_TOO_LARGE;
   p.qweight = (const uint8_t*)a.qweight;
   p.meta = (const uint8_t*)a.meta;
@@ -1294,13 +1392,14 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     p.dcols = p.cols <= 64 ? 64 : 128;
     p.nclass = p.cols <= 64 ? 4 : 3;
     p.x_stages = p.cols <= 64 ? 4 : 3;
-    p.w_stages = 3;
+    p.w_stages = p.cols <= 64 ? 3 : DZ_W_STAGES_WIDE;
     const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + 2 * kNumWG * kWinBytes;
-    p.r_per_class = min(4, (kSmemBudget - fixed) / (p.nclass * kRStage));
+    const int rstage = rstage_bytes(a.bits);
+    p.r_per_class = min(DZ_MAX_R_PER_CLASS, (kSmemBudget - fixed) / (p.nclass * rstage));
     if (p.r_per_class < 2 || p.nclass * p.r_per_class > kMaxR) return DZ_ERR_UNSUPPORTED;
     rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols, dt);
     if (rc) return rc;
-    const size_t smem = (size_t)fixed + (size_t)p.nclass * p.r_per_class * kRStage + 1024;
+    const size_t smem = (size_t)fixed + (size_t)p.nclass * p.r_per_class * rstage + 1024;
     auto kern = dt ? ((a.bits == 2) ? sbmm_tc_kernel<2, 1> : sbmm_tc_kernel<4, 1>)
                    : ((a.bits == 2) ? sbmm_tc_kernel<2, 0> : sbmm_tc_kernel<4, 0>);
     if (!di.attr_set[kidx]) {

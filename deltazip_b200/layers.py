@@ -72,7 +72,7 @@ class ColumnParallelLinear(_ParallelLinearBase):
         self.gather_output = gather_output
 
     def forward(self, x):
-        y = ops.base_gemm(x, self.weight)
+        y = ops.base_gemm(x, self.weight, stable=True)       # base weights are static
         return (tensor_model_parallel_all_gather(y) if self.gather_output else y), None
 
 
@@ -135,7 +135,7 @@ class RowParallelLinear(_ParallelLinearBase):
     def forward(self, x):
         if not self.input_is_parallel:
             x = x[..., self.shard[0]:self.shard[1]].contiguous()
-        y = ops.base_gemm(x, self.weight)
+        y = ops.base_gemm(x, self.weight, stable=True)
         if self.reduce_results and self.tp_size > 1:
             y = tensor_model_parallel_all_reduce(y)
         return y, None
@@ -183,6 +183,7 @@ class BaseLayerWithDelta(nn.Module):
         self.qweight_stacked[index] = 0
         self.scales_stacked[index] = 0
         self.meta_stacked[index] = 0
+        ops.stream_fence()        # slot writers never directly precede a forward pass's SBMM
 
     def set_delta(self, index: int, bitwidth: int, qweight: torch.Tensor,
                   qzeros: Optional[torch.Tensor], scales: torch.Tensor,
@@ -198,6 +199,7 @@ class BaseLayerWithDelta(nn.Module):
             self.scales_stacked[index].copy_(scales.reshape(self.scales_stacked[index].shape),
                                              non_blocking=ASYNC_COPY)
             self.meta_stacked[index].copy_(meta, non_blocking=ASYNC_COPY)
+            ops.stream_fence()
         else:
             dev = self.qweight_stacked.device
             ops.convert_from_gptq(qweight.to(dev, non_blocking=True), qzeros.to(dev, non_blocking=True),
@@ -222,8 +224,11 @@ class BaseLayerWithDelta(nn.Module):
             raise ValueError("bias is not supported by the delta layers")
         w = self.base_layer.linear_weights["weight"]
         if self.segments is not None:
+            # weights are static, slots change only through set_delta / reset_delta / the
+            # manager's uploads (all followed by a fence or an event wait) and the table is
+            # built by dz_build_segments: the early-start form of the kernel applies
             return ops.sbmm(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
-                            self.segments, w, out=out, bits=self.bits)
+                            self.segments, w, out=out, bits=self.bits, stable=True)
         y = ops.apply_delta(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked,
                             self.indices[: self.indices_len[0]], w)
         if out is not None:

@@ -503,6 +503,7 @@ class DeltaModelManager:
                     module.meta_stacked[index].copy_(d.meta.reshape(module.meta_stacked[index].shape),
                                                      non_blocking=True)
                     self.uploads += 3
+                ops.stream_fence()
         ev = torch.cuda.Event()
         ev.record(self.copy_stream)
         self._slot_ready[index] = ev
@@ -553,6 +554,7 @@ class DeltaModelManager:
         self._active_deltas[delta_id] = None
         for module in self.modules.values():
             module.bitwidth[index] = self.delta_config.max_bitwidth
+        ops.stream_fence()        # the caller's slot writes never directly precede an SBMM
         self._last_mapping = None
 
     def deactivate_delta(self, delta_id: int) -> bool:

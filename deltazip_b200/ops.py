@@ -184,11 +184,15 @@ def _bits_from_shapes(qweight_stacked: torch.Tensor, k: int) -> int:
 def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
          meta_stacked: torch.Tensor, segments: Segments, base_weight: Optional[torch.Tensor],
          out: Optional[torch.Tensor] = None, bits: Optional[int] = None,
-         _entry: str = "dz_sbmm", accumulate: bool = False) -> torch.Tensor:
+         _entry: str = "dz_sbmm", accumulate: bool = False, stable: bool = False) -> torch.Tensor:
     """y = x W^T + x dequant(delta_slot(i))^T with a prebuilt segment table.  With
     `base_weight=None` only the delta products are computed (rows of slot -1 get 0).
     `out` may be a column slice [:, a:a+N] of a wider row-major tensor; with
-    `accumulate=True` the result is added to `out` inside the kernel."""
+    `accumulate=True` the result is added to `out` inside the kernel.  `stable=True` is the
+    caller's statement that the base weight, the slot stacks and the segment table were not
+    written by the operation right before this call on the stream (DZ_SBMM_INPUTS_STABLE): the
+    kernel then starts loading them while its predecessor finishes.  After writing any of them
+    with a torch op, call `stream_fence()` before relying on it."""
     _need_cuda(x, qweight_stacked, scales_stacked, meta_stacked)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
@@ -226,15 +230,20 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
         segments=segments.buf.data_ptr(), y=out2.data_ptr(),
         M=m, N=n, K=k, num_slots=qweight_stacked.shape[0], bits=bits, dtype=_dtype_code(x),
         tokens_sorted=int(segments.sorted),
-        flags=_lib.DZ_SBMM_ACCUMULATE if accumulate else 0,
+        flags=(_lib.DZ_SBMM_ACCUMULATE if accumulate else 0) | (_lib.DZ_SBMM_INPUTS_STABLE if stable else 0),
         workspace=ws.data_ptr(), workspace_bytes=ws.numel(),
         y_stride=max(out2.stride(0), n))
     check(getattr(lib(), _entry)(ctypes.byref(args), _stream()), _entry)
     return out.reshape(*x.shape[:-1], n) if out.is_contiguous() else out
 
 
+def stream_fence() -> None:
+    """Separates earlier writers on the current stream from later `stable=True` SBMM calls."""
+    check(lib().dz_stream_fence(_stream()), "dz_stream_fence")
+
+
 def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out: Optional[torch.Tensor] = None, stable: bool = False) -> torch.Tensor:
     """y = x W^T on the same kernel (every token base-only)."""
     _need_cuda(x, base_weight)
     x2 = x.reshape(-1, x.shape[-1])
@@ -249,6 +258,7 @@ def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
     ws = _workspace(x.device, lib().dz_sbmm_workspace_bytes(m, n, k, 1))
     args = SbmmArgs(x=x2.data_ptr(), w_base=base_weight.data_ptr(), y=out.data_ptr(),
                     M=m, N=n, K=k, num_slots=0, bits=4, dtype=_dtype_code(x), tokens_sorted=1,
+                    flags=_lib.DZ_SBMM_INPUTS_STABLE if stable else 0,
                     workspace=ws.data_ptr(), workspace_bytes=ws.numel())
     check(lib().dz_base_gemm(ctypes.byref(args), _stream()), "dz_base_gemm")
     return out.reshape(*x.shape[:-1], n)

@@ -147,10 +147,22 @@ typedef struct {
 
 /* flags of dz_sbmm_args */
 enum {
-  DZ_SBMM_ACCUMULATE = 1    /* y += result instead of y = result: the in-place form
+  DZ_SBMM_ACCUMULATE = 1,   /* y += result instead of y = result: the in-place form
                                of the reference's GPTQ-layout ops (add_delta,
                                serving/vllm/delta/deltazip.py:14-38); the sum is
                                formed in fp32 and rounded once                    */
+  DZ_SBMM_INPUTS_STABLE = 2 /* the caller states that w_base, the slot stacks and the
+                               segment table were NOT written by the operation that
+                               immediately precedes this call in the stream (true for
+                               every layer call of a decode step: weights are static
+                               and the table is built once per step).  The kernel then
+                               loads them while its predecessor is still finishing and
+                               waits for the predecessor only before it touches x.
+                               Tables built by dz_build_segments and slots written by
+                               dz_convert_from_gptq / dz_slot_reset always qualify
+                               (those calls end with a stream fence); after other
+                               writers (e.g. a framework's copy kernel) call
+                               dz_stream_fence first or leave the flag off            */
 };
 
 size_t dz_sbmm_workspace_bytes(int M, int N, int K, int tokens_sorted);
@@ -278,6 +290,11 @@ int dz_allreduce_run(dz_allreduce_ctx* ctx, const void* in, void* out, int64_t c
                      int dtype, void* stream);
 int dz_allreduce_status(dz_allreduce_ctx* ctx, int* status);
 int dz_allreduce_destroy(dz_allreduce_ctx* ctx);
+
+/* Enqueues an empty kernel: whatever was enqueued before it has completed, with its writes
+ * visible, before any later kernel's early (pre-dependency) part can start.  See
+ * DZ_SBMM_INPUTS_STABLE. */
+int dz_stream_fence(void* stream);
 
 /* Reads and clears a device status word (synchronises `stream`). */
 int dz_read_status(int* status_word, void* stream, int* host_out);
