@@ -176,13 +176,16 @@ def allreduce_selfcheck(car, rank, world, device):
     # difference is kept and the verdict is agreed on at the end
     bad = None
     g = torch.Generator(device=device).manual_seed(100 + rank)
-    for dtype in (torch.float16, torch.bfloat16, torch.float32):
-        for numel in (8, 4096, 64 * 4096, 256 * 5120, 1 << 20):
-            x = torch.randn(numel, generator=g, device=device).to(dtype)
-            want = expected(x)
-            got = car.all_reduce(x)
-            if bad is None and not torch.equal(got, want):
-                bad = f"mismatch dtype={dtype} numel={numel}"
+    for variant in (1, 2):                   # the one-shot and the two-stage kernel, forced in turn
+        car.set_variant(variant)
+        for dtype in (torch.float16, torch.bfloat16, torch.float32):
+            for numel in (8, 4096, 64 * 4096, 8 * 1237, 256 * 5120, 1 << 20):
+                x = torch.randn(numel, generator=g, device=device).to(dtype)
+                want = expected(x)
+                got = car.all_reduce(x)
+                if bad is None and not torch.equal(got, want):
+                    bad = f"mismatch variant={variant} dtype={dtype} numel={numel}"
+    car.set_variant(0)                       # from here on: chosen by size and rank count
     for it in range(100):                    # produced directly in the staging buffer
         st = car.staging_like((TOKENS, HIDDEN), torch.float16)
         st.copy_(torch.randn((TOKENS, HIDDEN), generator=g, device=device).half())
@@ -214,12 +217,14 @@ def run_ours(args):
     car = None
     ar_check = None
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=device)
         if args.allreduce == "custom":
             # the library's peer-memory all-reduce for the row-parallel outputs
             from deltazip_b200 import custom_all_reduce
             car = custom_all_reduce.init_custom_ar(rank, world)
             ar_check = allreduce_selfcheck(car, rank, world, device)
+            car.set_variant(args.ar_variant)
     tp = world
     L = _lib.lib()
 
@@ -414,7 +419,10 @@ def run_ours(args):
                 "tokens": TOKENS, "deltas": NUM_DELTAS, "active_deltas": active, "bits": BITS,
                 "layers": args.layers, "sbmm_calls_per_step": n_calls,
                 "parallelism": f"tp{world}",
-                "allreduce": ("peer-memory (dz_allreduce_run)" if car is not None
+                "allreduce": ("peer-memory (dz_allreduce_run, %s)" % (
+                                  {0: "one-shot kernel at this size", 1: "one-shot kernel (forced)",
+                                   2: "two-stage kernel (forced)"}[args.ar_variant])
+                              if car is not None
                               else ("nccl" if world > 1 else "none")),
                 "l2": "inputs larger than L2: each step streams %.1f GB of distinct weights"
                       % (step_bytes * 1e-9),
@@ -957,6 +965,8 @@ def main():
                          "profiling captures and smoke runs)")
     ap.add_argument("--allreduce", default="custom", choices=["custom", "nccl"],
                     help="N>1: all-reduce after the row-parallel layers (library peer-memory kernel or NCCL)")
+    ap.add_argument("--ar-variant", type=int, default=0, choices=[0, 1, 2],
+                    help="peer-memory all-reduce kernel: 0 by size (default), 1 one-shot, 2 two-stage")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")
     ap.add_argument("--duration", type=float, default=None,
                     help="config 5: seconds of simulated arrivals (default 300)")

@@ -99,6 +99,7 @@ _SIGNATURES = {
     "dz_allreduce_staging": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),
     "dz_allreduce_run": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "dz_allreduce_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "dz_allreduce_set_variant": (c_int, [c_void_p, c_int]),
     "dz_allreduce_destroy": (c_int, [c_void_p]),
 }
 

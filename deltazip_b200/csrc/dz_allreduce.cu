@@ -17,6 +17,14 @@
 //     while a peer may still read it.
 //   * all ranks add in the same order, so every rank gets bit-identical results.
 //
+// Larger messages on more ranks use a second, two-stage kernel with the same flag protocol
+// (the reference switches the same way, serving/csrc/custom_all_reduce.cuh:443-456, kernels
+// :181-250): the message is cut into `world` parts; (A) rank r sums part r of all ranks' staging
+// buffers and puts the sum back into part r of its own staging buffer (nobody else reads that
+// part in stage A), (B) publishes it with a second flag and every rank collects the reduced
+// parts of all peers.  Each rank then pulls 2 (world-1)/world of the message over NVLink
+// instead of (world-1) times the message.
+//
 // A wait that does not complete within the time limit records DZ_ERR_TIMEOUT in the region's
 // status word and the kernel returns without reducing; nothing spins forever.
 // No multicast objects are used, only ordinary peer loads and stores.
@@ -37,6 +45,7 @@ struct dz_allreduce_ctx {
   bool imported[8] = {false};
   unsigned epoch = 0;                      // calls so far
   bool connected = false;
+  int force_variant = 0;                   // 0: by size, 1: one-shot, 2: two-stage (tests / tuning)
 };
 
 namespace dz {
@@ -47,7 +56,9 @@ constexpr int kMaxBlocks = 64;
 constexpr int kArThreads = 512;
 constexpr size_t kStatusOff = 0;                        // int status
 constexpr size_t kFlagsOff = 4096;                      // uint32 flag[kMaxWorld][kMaxBlocks]
+constexpr size_t kFlags2Off = 4096 + 2048;              // second table (two-stage kernel, stage B)
 constexpr size_t kStagingOff = 8192;
+static_assert(kMaxWorld * kMaxBlocks * 4 <= 2048, "flag tables are 2 KB each");
 constexpr unsigned long long kArTimeoutNs = 1000ull * 1000 * 1000;
 
 struct ArParams {
@@ -216,8 +227,106 @@ allreduce_oneshot_kernel(const ArParams p) {
   }
 }
 
+// Publishes `epoch` in table `flags_off`, entry [rank][b], of every peer and waits (bounded) until
+// every peer's entry [peer][b] of the own table holds it.  Called by the first WORLD threads.
+template <int WORLD>
+__device__ __forceinline__ void publish_and_wait(const ArParams& p, size_t flags_off, int b,
+                                                 bool fence_first, int* s_abort) {
+  if (threadIdx.x < WORLD && (int)threadIdx.x != p.rank) {
+    const int peer = threadIdx.x;
+    uint8_t* const mine = p.peers[p.rank];
+    unsigned* remote = reinterpret_cast<unsigned*>(p.peers[peer] + flags_off) + p.rank * kMaxBlocks + b;
+    // the block's stores were ordered before this thread by the preceding __syncthreads(); the
+    // system-scope release makes them visible to the peer before the flag
+    (void)fence_first;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
+    const unsigned* local = reinterpret_cast<const unsigned*>(mine + flags_off) + peer * kMaxBlocks + b;
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+      unsigned seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(local) : "memory");
+      if ((int)(seen - p.epoch) >= 0) break;
+      if ((it & 255u) == 255u) {
+        const unsigned long long now = ar_globaltimer();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > kArTimeoutNs) {
+          *s_abort = 1;
+          atomicCAS(reinterpret_cast<int*>(mine + kStatusOff), 0, (int)DZ_ERR_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+}
+
+// Two-stage form.  Vectors [0, nvec) are cut into WORLD parts of P = ceil(nvec / WORLD) vectors
+// and every part into gridDim.x sub-slices; block b works on sub-slice b of every part.
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(kArThreads)
+allreduce_twostage_kernel(const ArParams p) {
+  __shared__ int s_abort;
+  const int b = blockIdx.x, nb = gridDim.x;
+  const long long nvec = p.count / Vec<T>::kN;
+  const long long P = (nvec + WORLD - 1) / WORLD;
+  const long long S = (P + nb - 1) / nb;
+  uint8_t* const mine = p.peers[p.rank];
+  uint4* const my_stage =
+      reinterpret_cast<uint4*>(mine + kStagingOff + (size_t)p.parity * p.staging_bytes);
+  if (threadIdx.x == 0) s_abort = 0;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // sub-slice b of part r: [lo(r), hi(r))
+  auto lo = [&](int r) { return min(nvec, min((long long)r * P + (long long)b * S, (long long)(r + 1) * P)); };
+  auto hi = [&](int r) { return min(nvec, min((long long)r * P + (long long)(b + 1) * S, (long long)(r + 1) * P)); };
+
+  // copy-in: this block stages its sub-slice of every part
+  if (p.copy_in) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.in);
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r)
+      for (long long i = lo(r) + threadIdx.x; i < hi(r); i += kArThreads) my_stage[i] = src[i];
+  }
+  __syncthreads();
+  publish_and_wait<WORLD>(p, kFlagsOff, b, p.copy_in != 0, &s_abort);
+  __syncthreads();
+  if (s_abort) return;
+
+  // stage A: sum of sub-slice b of part `rank` over the ranks, in rank order, into the own buffer
+  const uint4* stage[WORLD];
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r)
+    stage[r] = reinterpret_cast<const uint4*>(p.peers[r] + kStagingOff +
+                                              (size_t)p.parity * p.staging_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(p.out);
+  for (long long i = lo(p.rank) + threadIdx.x; i < hi(p.rank); i += kArThreads) {
+    uint4 v[WORLD];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) v[r] = ld_peer(stage[r] + i);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) Vec<T>::add(acc, v[r]);
+    const uint4 sum = Vec<T>::pack(acc);
+    my_stage[i] = sum;       // only this rank reads part `rank` of its own buffer in stage A
+    dst[i] = sum;
+  }
+  __syncthreads();
+  // stage B: the reduced sub-slice is visible to the peers before the second flag
+  publish_and_wait<WORLD>(p, kFlags2Off, b, true, &s_abort);
+  __syncthreads();
+  if (s_abort) return;
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r) {
+    if (r == p.rank) continue;
+    for (long long i = lo(r) + threadIdx.x; i < hi(r); i += kArThreads) dst[i] = ld_peer(stage[r] + i);
+  }
+}
+
 template <typename T>
-cudaError_t launch_allreduce(const ArParams& p, int blocks, cudaStream_t st) {
+cudaError_t launch_allreduce(const ArParams& p, int blocks, bool two_stage, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(kArThreads);
@@ -227,6 +336,16 @@ cudaError_t launch_allreduce(const ArParams& p, int blocks, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (two_stage) {
+    switch (p.world) {
+      case 3: return cudaLaunchKernelEx(&cfg, allreduce_twostage_kernel<T, 3>, p);
+      case 4: return cudaLaunchKernelEx(&cfg, allreduce_twostage_kernel<T, 4>, p);
+      case 5: return cudaLaunchKernelEx(&cfg, allreduce_twostage_kernel<T, 5>, p);
+      case 6: return cudaLaunchKernelEx(&cfg, allreduce_twostage_kernel<T, 6>, p);
+      case 7: return cudaLaunchKernelEx(&cfg, allreduce_twostage_kernel<T, 7>, p);
+      default: return cudaLaunchKernelEx(&cfg, allreduce_twostage_kernel<T, 8>, p);
+    }
+  }
   switch (p.world) {
     case 1: return cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<T, 1>, p);
     case 2: return cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<T, 2>, p);
@@ -329,13 +448,33 @@ int dz_allreduce_run(dz_allreduce_ctx* c, const void* in, void* out, int64_t cou
   p.copy_in = (in != staging) ? 1 : 0;
   p.epoch = ++c->epoch;
   p.staging_bytes = c->max_bytes;
-  // one block per 8 KB (one vector per thread and rank), at most kMaxBlocks; every rank
-  // computes the same number
-  int blocks = (int)((bytes + 8191) / 8192);
+  // One-shot for the sizes the row-parallel layers produce at decode (0.5 - 2.6 MB at 64 - 256
+  // tokens), two-stage above.  The reference switches at 512 KB (up to 4 ranks) / 256 KB (up to
+  // 8); measured on B200 / NVLink 5 the two extra latency-bound phases of the two-stage form
+  // cost more than the traffic they save until the message reaches several MB (4 ranks,
+  // 512 KB: 13 us one-shot against 33 us two-stage).  Every rank computes the same choice and
+  // the same block count.
+  bool two_stage = c->world > 2 && bytes >= (size_t)4 * 1024 * 1024;
+  if (c->force_variant == 1) two_stage = false;
+  if (c->force_variant == 2 && c->world > 2) two_stage = true;
+  int blocks;
+  if (two_stage) {
+    // every block handles one sub-slice (~4 KB) of each of the `world` parts
+    blocks = (int)((bytes / c->world + 4095) / 4096);
+  } else {
+    // one block per 8 KB (one vector per thread and rank)
+    blocks = (int)((bytes + 8191) / 8192);
+  }
   blocks = blocks < 1 ? 1 : (blocks > kMaxBlocks ? kMaxBlocks : blocks);
-  if (dtype == DZ_DTYPE_F16) DZ_CUDA_OK(launch_allreduce<__half>(p, blocks, st));
-  else if (dtype == DZ_DTYPE_BF16) DZ_CUDA_OK(launch_allreduce<__nv_bfloat16>(p, blocks, st));
-  else DZ_CUDA_OK(launch_allreduce<float>(p, blocks, st));
+  if (dtype == DZ_DTYPE_F16) DZ_CUDA_OK(launch_allreduce<__half>(p, blocks, two_stage, st));
+  else if (dtype == DZ_DTYPE_BF16) DZ_CUDA_OK(launch_allreduce<__nv_bfloat16>(p, blocks, two_stage, st));
+  else DZ_CUDA_OK(launch_allreduce<float>(p, blocks, two_stage, st));
+  return DZ_OK;
+}
+
+int dz_allreduce_set_variant(dz_allreduce_ctx* c, int variant) {
+  if (!c || variant < 0 || variant > 2) return DZ_ERR_INVALID_ARG;
+  c->force_variant = variant;
   return DZ_OK;
 }
 

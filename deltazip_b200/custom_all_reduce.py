@@ -79,6 +79,11 @@ class CustomAllreduce:
                                      _DTYPES[inp.dtype], stream), "dz_allreduce_run")
         return out
 
+    def set_variant(self, variant: int) -> None:
+        """0: kernel chosen by message size and rank count; 1: always the one-shot kernel;
+        2: the two-stage kernel whenever there are more than two ranks (all ranks alike)."""
+        check(lib().dz_allreduce_set_variant(self._ctx, variant), "dz_allreduce_set_variant")
+
     def status(self) -> int:
         st = ctypes.c_int()
         check(lib().dz_allreduce_status(self._ctx, ctypes.byref(st)), "dz_allreduce_status")

@@ -289,6 +289,11 @@ int dz_allreduce_staging(dz_allreduce_ctx* ctx, void** ptr, size_t* bytes);
 int dz_allreduce_run(dz_allreduce_ctx* ctx, const void* in, void* out, int64_t count,
                      int dtype, void* stream);
 int dz_allreduce_status(dz_allreduce_ctx* ctx, int* status);
+/* Kernel choice of later runs: 0 = by message size and rank count (one kernel that sums whole
+ * slices for small messages, a reduce-scatter + all-gather kernel above the sizes at which
+ * serving/csrc/custom_all_reduce.cuh:443-456 switches), 1 = always the former, 2 = the latter
+ * whenever there are more than two ranks.  Every rank must make the same choice. */
+int dz_allreduce_set_variant(dz_allreduce_ctx* ctx, int variant);
 int dz_allreduce_destroy(dz_allreduce_ctx* ctx);
 
 /* Enqueues an empty kernel: whatever was enqueued before it has completed, with its writes

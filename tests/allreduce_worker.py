@@ -38,8 +38,11 @@ def main():
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     # --- sizes x dtypes, out of place, bit-exact against the rank-order fp32 sum ---
-    for dtype in (torch.float16, torch.bfloat16, torch.float32):
-        for numel in (8, 4096, 64 * 4096, 1000 * 8, 2 * 1024 * 1024):
+    # (both kernels forced in turn -- one-shot and reduce-scatter + all-gather -- then the
+    # size-based choice; ragged sizes exercise uneven parts and sub-slices)
+    for variant, dtype in [(v, d) for v in (1, 2, 0) for d in (torch.float16, torch.bfloat16, torch.float32)]:
+        h.set_variant(variant)
+        for numel in (8, 4096, 64 * 4096, 1000 * 8, 8 * 1237, 2 * 1024 * 1024):
             x = torch.randn(numel, device=dev, dtype=torch.float32, generator=g).to(dtype)
             parts = [torch.empty_like(x) for _ in range(world)]
             dist.all_gather(parts, x)
@@ -62,6 +65,7 @@ def main():
     # --- staging path + many back-to-back calls with changing data (buffer alternation) ---
     shape = (64, 4096)
     for it in range(200):
+        h.set_variant(1 + (it // 25) % 2)       # alternate the two kernels every 25 calls
         st = h.staging_like(shape, torch.float16)
         st.copy_(torch.full(shape, float(rank + 1 + (it % 7)), device=dev, dtype=torch.float16))
         out = h.all_reduce(st)
@@ -70,6 +74,7 @@ def main():
             assert torch.equal(out, torch.full(shape, want, device=dev, dtype=torch.float16)), it
     torch.cuda.synchronize()
     assert h.status() == 0
+    h.set_variant(0)
 
     # --- row-parallel delta layer under tensor parallelism vs the unsharded layer ---
     n, k, slots, bits, m = 512, 1024, 4, 4, 48
