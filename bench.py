@@ -217,7 +217,6 @@ def run_ours(args):
     car = None
     ar_check = None
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=device)
         if args.allreduce == "custom":
             # the library's peer-memory all-reduce for the row-parallel outputs

@@ -80,6 +80,9 @@ _SIGNATURES = {
     "dz_sbmm_static_status": (c_int, [c_void_p, POINTER(c_int)]),
     "dz_delta_embedding": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "dz_grouped_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "dz_grouped_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_int64, c_void_p, c_size_t, c_void_p]),
     "dz_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "dz_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "dz_rotary_and_cache": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

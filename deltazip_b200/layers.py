@@ -22,7 +22,7 @@ from .config import DeltaConfig
 from .custom_all_reduce import get_handle as get_custom_ar_handle
 from .parallel_state import (get_tensor_model_parallel_rank, get_tensor_model_parallel_world_size,
                              SHARD_UNIT, shard_range, tensor_model_parallel_all_gather,
-                             tensor_model_parallel_all_reduce)
+                             tensor_model_parallel_all_reduce, tensor_model_parallel_gather)
 
 ASYNC_COPY = True
 
@@ -314,8 +314,195 @@ class RowParallelLinearWithDelta(BaseLayerWithDelta):
         return type(source_layer) is RowParallelLinear
 
 
+# ---------------------------------------------------------------------------
+# embedding and output matrix: a full replacement matrix per delta
+# ---------------------------------------------------------------------------
+
+class VocabParallelEmbedding(nn.Module):
+    """Token embedding with the vocabulary rows split over the ranks at 128-row units (what the
+    delta layer reads of serving/vllm/model_executor/layers/vocab_parallel_embedding.py:47-113)."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, full_weight: Optional[torch.Tensor] = None,
+                 device="cuda", dtype=torch.float16):
+        super().__init__()
+        rank, size = get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size()
+        self.org_vocab_size = self.num_embeddings = num_embeddings
+        self.embedding_dim = embedding_dim
+        self.tp_size = size
+        unit = SHARD_UNIT if num_embeddings % SHARD_UNIT == 0 else 1
+        self.vocab_start_index, self.vocab_end_index = shard_range(num_embeddings, unit, rank, size)
+        self.shard_sizes = [hi - lo for lo, hi in (shard_range(num_embeddings, unit, r, size)
+                                                   for r in range(size))]
+        rows = self.vocab_end_index - self.vocab_start_index
+        if full_weight is None:
+            w = torch.empty((rows, embedding_dim), dtype=dtype, device=device).normal_(0, 1.0)
+        else:
+            w = full_weight[self.vocab_start_index:self.vocab_end_index].to(device=device, dtype=dtype).contiguous()
+        self.weight = nn.Parameter(w, requires_grad=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_size == 1:
+            return self.weight[x]
+        outside = (x < self.vocab_start_index) | (x >= self.vocab_end_index)
+        local = (x - self.vocab_start_index).masked_fill(outside, 0)
+        out = self.weight[local]
+        out[outside] = 0
+        return tensor_model_parallel_all_reduce(out)
+
+
+class ParallelLMHead(VocabParallelEmbedding):
+    """Output matrix, vocabulary-parallel; its weight is handed to the logits processor."""
+
+
+class LogitsProcessor(nn.Module):
+    """hidden states -> logits over the whole vocabulary on rank 0 (None elsewhere), scaled: what
+    the delta layer needs of serving/vllm/model_executor/layers/logits_processor.py:14-84."""
+
+    def __init__(self, vocab_size: int, org_vocab_size: Optional[int] = None, scale: float = 1.0,
+                 logits_as_input: bool = False):
+        super().__init__()
+        self.vocab_size, self.org_vocab_size = vocab_size, org_vocab_size or vocab_size
+        self.scale, self.logits_as_input = scale, logits_as_input
+        self.include_gpu_probs_tensor = False
+        self.shard_sizes: Optional[list] = None
+
+    def forward(self, embedding: torch.Tensor, hidden_states: torch.Tensor,
+                embedding_bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        logits = hidden_states if self.logits_as_input else \
+            self._get_logits(hidden_states, embedding, embedding_bias)
+        if logits is not None:
+            logits = logits[..., : self.org_vocab_size]
+            if self.scale != 1.0:
+                logits = logits * self.scale
+        return logits
+
+    def _get_logits(self, hidden_states, embedding, embedding_bias=None):
+        logits = ops.base_gemm(hidden_states, embedding) if embedding.shape[0] % 128 == 0 \
+            else hidden_states @ embedding.t()
+        if embedding_bias is not None:
+            logits = logits + embedding_bias
+        return tensor_model_parallel_gather(logits, sizes=self.shard_sizes)
+
+
+class VocabParallelEmbeddingWithDelta(nn.Module):
+    """Embedding with a replacement table per delta (serving/vllm/delta/layers_marlin.py:97-171):
+    a token of slot d reads delta_weights[d], a base-model token the base table; under tensor
+    parallelism every rank looks up the ids of its own vocabulary rows and the rows are summed."""
+
+    def __init__(self, base_layer: VocabParallelEmbedding) -> None:
+        super().__init__()
+        self.base_layer = base_layer
+        self.tp_size = get_tensor_model_parallel_world_size()
+        self.tp_rank = get_tensor_model_parallel_rank()
+        self.vocab_start_index = base_layer.vocab_start_index
+        self.vocab_end_index = base_layer.vocab_end_index
+        self.indices = self.embeddings_indices = self.indices_len = None
+
+    def create_delta_weights(self, max_deltas: int, delta_config: DeltaConfig, model_config=None) -> None:
+        w = self.base_layer.weight
+        self.delta_weights = torch.zeros((max_deltas, *w.shape), dtype=w.dtype, device=w.device)
+        self.bitwidth = [0] * max_deltas
+
+    def reset_delta(self, index: int):
+        self.bitwidth[index] = 0
+        self.delta_weights[index] = 0
+
+    def set_delta(self, index: int, bitwidth: int, weight: torch.Tensor):
+        """`weight`: this rank's rows of the delta's table (the reference's per-rank files)."""
+        self.bitwidth[index] = bitwidth
+        self.delta_weights[index].copy_(weight, non_blocking=ASYNC_COPY)
+        ops.stream_fence()
+
+    def set_mapping(self, base_indices, sampler_indices=None, sampler_indices_padded=None,
+                    embeddings_indices=None, indices_len=None, segments=None):
+        self.indices, self.embeddings_indices, self.indices_len = base_indices, embeddings_indices, indices_len
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        indices = self.indices[: self.indices_len[0]]
+        if self.tp_size > 1:
+            outside = (x < self.vocab_start_index) | (x >= self.vocab_end_index)
+            local = (x - self.vocab_start_index).masked_fill(outside, 0)
+        else:
+            local = x
+        out = ops.apply_delta_embed(local, self.delta_weights, indices, self.base_layer.weight)
+        if self.tp_size > 1:
+            out[outside] = 0
+            out = tensor_model_parallel_all_reduce(out)
+        return out
+
+    @classmethod
+    def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
+        return type(source_layer) is VocabParallelEmbedding
+
+
+class LogitsProcessorWithDelta(nn.Module):
+    """Logits with a replacement output matrix per delta (layers_marlin.py:614-726): the rows of
+    a sequence of slot d are multiplied by weight_stacked[d], base-model rows by the base
+    matrix -- one grouped launch (ops.apply_delta_uncompressed) -- and the vocabulary shards are
+    gathered on rank 0."""
+
+    def __init__(self, base_layer: LogitsProcessor, hidden_size: int, dtype: torch.dtype, device) -> None:
+        super().__init__()
+        self.base_layer = base_layer
+        self.hidden_size, self.dtype, self.device = hidden_size, dtype, device
+        self.tp_size = get_tensor_model_parallel_world_size()
+        self.tp_rank = get_tensor_model_parallel_rank()
+        self.indices = self.indices_padded = self.indices_len = None
+        self.rows: Optional[int] = None
+
+    logits_as_input = property(lambda self: self.base_layer.logits_as_input)
+    vocab_size = property(lambda self: self.base_layer.vocab_size)
+    scale = property(lambda self: self.base_layer.scale)
+    org_vocab_size = property(lambda self: self.base_layer.org_vocab_size)
+    include_gpu_probs_tensor = property(lambda self: self.base_layer.include_gpu_probs_tensor)
+    shard_sizes = property(lambda self: self.base_layer.shard_sizes)
+
+    def create_delta_weights(self, max_deltas: int, delta_config: DeltaConfig, model_config=None) -> None:
+        rows = self.rows if self.rows is not None else self.base_layer.vocab_size // self.tp_size
+        self.weight_stacked = torch.zeros((max_deltas, rows, self.hidden_size), dtype=self.dtype,
+                                          device=self.device)
+        self.bitwidth = [0] * max_deltas
+
+    def reset_delta(self, index: int):
+        self.weight_stacked[index] = 0
+        self.bitwidth[index] = 0
+
+    def set_delta(self, index: int, bitwidth: int, weight: torch.Tensor):
+        self.bitwidth[index] = bitwidth
+        self.weight_stacked[index].copy_(weight, non_blocking=ASYNC_COPY)
+        ops.stream_fence()
+
+    def set_mapping(self, base_indices, sampler_indices=None, sampler_indices_padded=None,
+                    embeddings_indices=None, indices_len=None, segments=None):
+        self.indices, self.indices_padded, self.indices_len = sampler_indices, sampler_indices_padded, indices_len
+
+    def _get_logits(self, hidden_states, embedding, embedding_bias=None):
+        logits = ops.apply_delta_uncompressed(hidden_states, self.weight_stacked,
+                                              self.indices[: self.indices_len[1]], embedding)
+        return tensor_model_parallel_gather(logits, sizes=self.shard_sizes)
+
+    def forward(self, *args, **kwargs):
+        return type(self.base_layer).forward(self, *args, **kwargs)
+
+    @classmethod
+    def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):
+        return False            # installed through from_layer_logits_processor, like the reference
+
+
+def from_layer_logits_processor(layer: LogitsProcessor, lm_head: ParallelLMHead, max_deltas: int,
+                                delta_config: DeltaConfig, model_config=None) -> LogitsProcessorWithDelta:
+    """The logits processor's delta layer, sized after the output matrix it will be used with
+    (layers_marlin.py:752-769)."""
+    layer.shard_sizes = lm_head.shard_sizes
+    ret = LogitsProcessorWithDelta(layer, lm_head.embedding_dim, lm_head.weight.dtype, lm_head.weight.device)
+    ret.rows = lm_head.weight.shape[0]
+    ret.create_delta_weights(max_deltas, delta_config, model_config)
+    return ret
+
+
 _all_delta_classes = (MergedQKVParallelLinearWithDelta, MergedColumnParallelLinearWithDelta,
-                      ColumnParallelLinearWithDelta, RowParallelLinearWithDelta)
+                      ColumnParallelLinearWithDelta, RowParallelLinearWithDelta,
+                      VocabParallelEmbeddingWithDelta)
 
 
 def from_layer(layer: nn.Module, max_deltas: int, delta_config: DeltaConfig,

@@ -30,7 +30,8 @@ import torch
 from . import ops
 from ._lib import check, lib
 from .config import CompressionConfig, DeltaConfig
-from .layers import BaseLayerWithDelta, DeltaMapping, from_layer
+from .layers import (BaseLayerWithDelta, DeltaMapping, LogitsProcessor, LogitsProcessorWithDelta,
+                     VocabParallelEmbeddingWithDelta, from_layer, from_layer_logits_processor)
 
 
 def _convert_mapping(mapping: DeltaMapping, delta_index_to_id: List[Optional[int]], max_deltas: int,
@@ -383,6 +384,8 @@ class DeltaModelManager:
         self._slot_ready: List[Optional[torch.cuda.Event]] = [None] * self.delta_slots
         self._slot_released: List[Optional[torch.cuda.Event]] = [None] * self.delta_slots
         self.layout = SlotLayout()
+        self.table_modules: Dict[str, torch.nn.Module] = {}   # embedding / logits layers (full tables)
+        self._slot_has_base_table: Dict[Tuple[str, int], bool] = {}
         self.arena: Optional[torch.Tensor] = None
         self.uploads = 0                                   # host-to-device copies issued so far
         self._create_delta_modules()
@@ -411,8 +414,20 @@ class DeltaModelManager:
             if leaf not in self.supported_delta_modules:
                 continue
             packed = self.packed_modules_mapping.get(leaf, [leaf])
+            if isinstance(module, LogitsProcessor) and hasattr(self.model, "lm_head"):
+                # the logits processor is sized after the output matrix it is used with
+                new = from_layer_logits_processor(module, self.model.lm_head, self.delta_slots,
+                                                  self.delta_config)
+                self._install(name, new)
+                self.table_modules[name] = new
+                continue
             new = from_layer(module, self.delta_slots, self.delta_config, packed, allocate=False)
             if new is module:
+                continue
+            if isinstance(new, VocabParallelEmbeddingWithDelta):
+                new.create_delta_weights(self.delta_slots, self.delta_config)
+                self._install(name, new)
+                self.table_modules[name] = new
                 continue
             n, k = module.weight.shape
             self.layout.add(name, n, k, self.delta_config.max_bitwidth)
@@ -429,14 +444,17 @@ class DeltaModelManager:
                        self.arena[:, mo:mo + mb].view(torch.int16).unflatten(1, ms),
                        self.arena[:, so:so + sb].view(torch.float16).unflatten(1, ss))
             new.create_delta_weights(self.delta_slots, self.delta_config, storage=storage)
-            parent = self.model
-            parts = name.split(".")
-            for p in parts[:-1]:
-                parent = getattr(parent, p)
-            setattr(parent, parts[-1], new)
+            self._install(name, new)
             self.modules[name] = new
-            new.set_mapping(self.base_indices, self.sampler_indices, self.sampler_indices_padded,
-                            self.embeddings_indices, self.indices_len, segments=self.segments)
+
+    def _install(self, name: str, new: torch.nn.Module) -> None:
+        parent = self.model
+        parts = name.split(".")
+        for p in parts[:-1]:
+            parent = getattr(parent, p)
+        setattr(parent, parts[-1], new)
+        new.set_mapping(self.base_indices, self.sampler_indices, self.sampler_indices_padded,
+                        self.embeddings_indices, self.indices_len, segments=self.segments)
 
     # -- registry ----------------------------------------------------------------
     def add_delta(self, delta: DeltaModel) -> bool:
@@ -504,6 +522,20 @@ class DeltaModelManager:
                                                      non_blocking=True)
                     self.uploads += 3
                 ops.stream_fence()
+        # replacement tables (embedding, output matrix) of deltas that carry them
+        with torch.cuda.stream(self.copy_stream):
+            for name, module in self.table_modules.items():
+                d = delta.get_delta(name) or delta.get_delta(name.replace("logits_processor", "lm_head"))
+                if d is not None and d.weight is not None:
+                    module.set_delta(index, delta.bitwidth, d.weight)
+                    self._slot_has_base_table[(name, index)] = False
+                elif not self._slot_has_base_table.get((name, index), False):
+                    # tables replace, they do not add: a delta without its own table serves
+                    # the base model's (copied once; later table-less deltas reuse the copy)
+                    base = self.model.lm_head.weight if isinstance(module, LogitsProcessorWithDelta) \
+                        else module.base_layer.weight
+                    module.set_delta(index, delta.bitwidth, base)
+                    self._slot_has_base_table[(name, index)] = True
         ev = torch.cuda.Event()
         ev.record(self.copy_stream)
         self._slot_ready[index] = ev

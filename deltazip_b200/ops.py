@@ -393,21 +393,52 @@ def apply_delta_embed(x: torch.Tensor, delta_weights: torch.Tensor, indices: tor
     return out.reshape(*x.shape, hidden)
 
 
+_gg_ws = {}
+
+
+def grouped_gemm(x: torch.Tensor, delta_weights: Optional[torch.Tensor], segments: Segments,
+                 base_weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[i] = x[i] T^T with T = base_weight [V, K] for rows of slot -1 and delta_weights[slot]
+    ([D, V, K], dense) otherwise, in one launch per 128 rows (dz_grouped_gemm)."""
+    _need_cuda(x, delta_weights, base_weight)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    v = base_weight.shape[0]
+    d = delta_weights.shape[0] if delta_weights is not None and delta_weights.numel() else 0
+    if d and (not delta_weights.is_contiguous() or tuple(delta_weights.shape[1:]) != (v, k)):
+        raise ValueError("delta_weights must be a contiguous [D, V, K] stack matching base_weight")
+    if segments.m != m or segments.num_slots != d:
+        raise ValueError("segment table does not match the batch / the number of slots")
+    if out is None:
+        out = torch.empty((m, v), dtype=x.dtype, device=x.device)
+    if m == 0:
+        return out.reshape(*x.shape[:-1], v)
+    need = lib().dz_grouped_gemm_workspace_bytes(m, k, int(segments.sorted))
+    key = (x.device.index, _stream())
+    ws = _gg_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 4096), dtype=torch.uint8, device=x.device)
+        _gg_ws[key] = ws
+    check(lib().dz_grouped_gemm(
+        x2.data_ptr(), base_weight.data_ptr(), delta_weights.data_ptr() if d else None,
+        v * k * 2 if d else 0, segments.buf.data_ptr(), out.data_ptr(), m, v, k, d, _dtype_code(x),
+        int(segments.sorted), out.stride(0), ws.data_ptr(), ws.numel(), _stream()), "dz_grouped_gemm")
+    return out.reshape(*x.shape[:-1], v)
+
+
 def apply_delta_uncompressed(x: torch.Tensor, delta_weights: torch.Tensor, indices: torch.Tensor,
                              base_embedding: torch.Tensor) -> torch.Tensor:
     """lm_head with a full replacement matrix per delta: rows with slot d are multiplied by
     delta_weights[d], rows with -1 by base_embedding (reference:
-    serving/vllm/delta/deltazip_marlin.py:21-53; like it, this loops over the distinct ids,
-    which costs one host synchronisation).  Each group runs on the dense tcgen05 GEMM."""
+    serving/vllm/delta/deltazip_marlin.py:21-53, a host loop over the distinct ids).  Here one
+    grouped launch on the dense tcgen05 GEMM, no host synchronisation; the vocabulary rows must
+    be a multiple of 128 (pad the matrices otherwise)."""
     _need_cuda(x, delta_weights, indices, base_embedding)
-    x2 = x.reshape(-1, x.shape[-1])
-    n = base_embedding.shape[0]
-    out = torch.zeros((x2.shape[0], n), dtype=x.dtype, device=x.device)
-    for d in torch.unique(indices).tolist():
-        rows = (indices == d).nonzero(as_tuple=True)[0]
-        w = base_embedding if d < 0 else delta_weights[d]
-        out[rows] = base_gemm(x2[rows].contiguous(), w.contiguous())
-    return out.reshape(*x.shape[:-1], n)
+    d = delta_weights.shape[0] if delta_weights is not None and delta_weights.numel() else 0
+    seg = _segments_for(indices, d, x.device)
+    return grouped_gemm(x, delta_weights if d else None, seg, base_embedding.contiguous())
 
 
 # ---------------------------------------------------------------------------

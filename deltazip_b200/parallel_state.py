@@ -75,6 +75,32 @@ def tensor_model_parallel_all_gather(x: torch.Tensor, dim: int = -1) -> torch.Te
     return torch.cat(parts, dim=dim)
 
 
+def tensor_model_parallel_gather(x: torch.Tensor, dst: int = 0, dim: int = -1,
+                                 sizes: Optional[list] = None) -> Optional[torch.Tensor]:
+    """Concatenation of every rank's `x` along `dim` on rank `dst`, None elsewhere (contract of
+    communication_op.py:74-104).  `sizes` gives every rank's extent along `dim` when the shards
+    are uneven (vocabulary rows cut at 128-row units): the pieces travel padded to the widest
+    and are trimmed on arrival."""
+    if _TP_SIZE == 1:
+        return x
+    if dim < 0:
+        dim += x.dim()
+    widest = max(sizes) if sizes else x.shape[dim]
+    piece = x
+    if x.shape[dim] != widest:
+        pad = list(x.shape)
+        pad[dim] = widest - x.shape[dim]
+        piece = torch.cat([x, x.new_zeros(pad)], dim=dim)
+    piece = piece.contiguous()
+    parts = [torch.empty_like(piece) for _ in range(_TP_SIZE)] if _TP_RANK == dst else None
+    dist.gather(piece, parts, dst=dst, group=_TP_GROUP)
+    if _TP_RANK != dst:
+        return None
+    if sizes:
+        parts = [p.narrow(dim, 0, n) for p, n in zip(parts, sizes)]
+    return torch.cat(parts, dim=dim)
+
+
 # Tensor-parallel cuts are made at whole 128-wide units on both sides of a column-parallel /
 # row-parallel pair (128 output rows of qkv / gate / up = 128 input columns of o_proj /
 # down_proj), so that a producer's shard is exactly its consumer's K range for every rank

@@ -210,6 +210,24 @@ int dz_delta_embedding(const int64_t* token_ids, const void* indices, int index_
                        int* status_word, void* stream);
 
 /*
+ * Layers with a full replacement matrix per delta (the output matrix / lm_head):
+ *   y[i] = x[i] T^T with T = base_matrix [V, K] for tokens of slot -1 and delta_matrices[slot]
+ *   (a dense stack [num_slots, V, K], matrix_stride_bytes = V*K*2) otherwise.
+ * One launch per 128 tokens serves all groups present in the batch; every present matrix is
+ * streamed once, matrices of slots without tokens are not read, nothing synchronises with the
+ * host.  `segments` is the batch's table (dz_build_segments over the per-row slot ids),
+ * tokens_sorted as for dz_sbmm, y [M, V] (rows y_stride elements apart, 0 = V).  V % 128 == 0,
+ * K % 64 == 0.  `workspace` >= dz_grouped_gemm_workspace_bytes(), zero-filled once; its first
+ * int is a status word (dz_read_status).  Replaces apply_delta_uncompressed
+ * (serving/vllm/delta/deltazip_marlin.py:21-53), which loops over the distinct ids on the host.
+ */
+size_t dz_grouped_gemm_workspace_bytes(int M, int K, int tokens_sorted);
+int dz_grouped_gemm(const void* x, const void* base_matrix, const void* delta_matrices,
+                    int64_t matrix_stride_bytes, const void* segments, void* y, int M, int V, int K,
+                    int num_slots, int dtype, int tokens_sorted, int64_t y_stride, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/*
  * The steps between the SBMM calls of a decoder layer at decode time, so that a decode step is a
  * chain of this library's launches.  2-byte elements of `dtype`; 16-byte aligned pointers; all
  * enqueue one kernel on `stream` and return.

@@ -255,3 +255,81 @@ def test_per_delta_embedding_and_lm_head():
         w = base if idx[i] < 0 else tabs[idx[i]]
         ref[i] = x[i].float() @ w.float().t()
     assert O.rel_l2(logits.float().cpu().numpy(), ref.cpu().numpy()) <= 2e-3
+
+
+class TablesModel(nn.Module):
+    """Embedding, one delta linear and the logits processor: the modules that carry full tables."""
+    supported_delta_modules = ["embed_tokens", "o_proj", "logits_processor"]
+    packed_modules_mapping = {}
+
+    def __init__(self, vocab=1024, hidden=256):
+        super().__init__()
+        from deltazip_b200 import layers as Ls
+        self.embed_tokens = Ls.VocabParallelEmbedding(vocab, hidden)
+        self.o_proj = Ls.RowParallelLinear(hidden, hidden)
+        self.lm_head = Ls.ParallelLMHead(vocab, hidden)
+        self.logits_processor = Ls.LogitsProcessor(vocab)
+
+
+def test_embedding_and_logits_layers_with_replacement_tables():
+    """VocabParallelEmbeddingWithDelta / LogitsProcessorWithDelta installed by the manager: a
+    delta that brings its own embedding and output matrix uses them for its rows, base-model rows
+    and deltas without tables use the base ones (reference semantics,
+    serving/vllm/delta/deltazip_marlin.py:21-86)."""
+    from deltazip_b200 import layers as Ls
+    from deltazip_b200.config import DeltaConfig
+    from deltazip_b200.models import DeltaLayerWeights, DeltaModel, DeltaModelManager
+    torch.manual_seed(3)
+    model = TablesModel()
+    mgr = DeltaModelManager(model, 16, 64, 1024, DeltaConfig(max_deltas=3, max_bitwidth=4))
+    assert isinstance(model.embed_tokens, Ls.VocabParallelEmbeddingWithDelta)
+    assert isinstance(model.logits_processor, Ls.LogitsProcessorWithDelta)
+    assert model.logits_processor.weight_stacked.shape == (3, 1024, 256)
+    g = torch.Generator().manual_seed(4)
+    tables = {}
+    for did in (1, 2):
+        emb = torch.randn((1024, 256), generator=g).half()
+        head = torch.randn((1024, 256), generator=g).half()
+        tables[did] = (emb.cuda(), head.cuda())
+        mgr.add_delta(DeltaModel(did, 4, {"embed_tokens": DeltaLayerWeights("embed_tokens", weight=emb),
+                                           "lm_head": DeltaLayerWeights("lm_head", weight=head)}))
+        mgr.activate_delta(did)
+    mgr.add_delta(DeltaModel(3, 4, {}))                      # a delta without tables
+    mgr.activate_delta(3)
+    ids = (0, 1, 1, 2, 3, 3, 0, 2)                            # per token == per sequence here
+    mgr.set_delta_mapping(Ls.DeltaMapping(ids, ids))
+    tok = torch.randint(0, 1024, (8,), generator=g).cuda()
+    h = model.embed_tokens(tok)
+    base_e, base_h = model.embed_tokens.base_layer.weight, model.lm_head.weight
+    for i, did in enumerate(ids):
+        want = tables[did][0][tok[i]] if did in tables else base_e[tok[i]]
+        assert torch.equal(h[i], want), i
+    x = torch.randn((8, 256), generator=g).half().cuda()
+    logits = model.logits_processor(model.lm_head.weight, x)
+    assert logits.shape == (8, 1024)
+    for i, did in enumerate(ids):
+        w = tables[did][1] if did in tables else base_h
+        ref = x[i].float() @ w.float().t()
+        assert ((logits[i].float() - ref).norm() / ref.norm()).item() <= 2e-3, i
+
+
+def test_grouped_gemm_many_groups_and_two_token_blocks():
+    """The grouped launch at output-matrix size: 32000 x 4096, 200 rows over 6 groups (base rows
+    included), unsorted rows; absent groups' matrices are never read (poisoned with NaN)."""
+    from deltazip_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(9)
+    vocab, hidden, d = 32000, 4096, 7
+    base = (torch.randn((vocab, hidden), generator=g, device="cuda") * 0.05).half()
+    tabs = (torch.randn((d, vocab, hidden), generator=g, device="cuda") * 0.05).half()
+    tabs[5] = float("nan")                                   # slot 5 has no rows
+    tabs[6] = float("nan")
+    idx = torch.randint(-1, 5, (200,), generator=g, device="cuda")
+    x = torch.randn((200, hidden), generator=g, device="cuda").half()
+    y = ops.apply_delta_uncompressed(x, tabs, idx, base)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all()
+    for s in range(-1, 5):
+        rows = (idx == s).nonzero().flatten()
+        w = base if s < 0 else tabs[s]
+        ref = x[rows].float() @ w.float().t()
+        assert ((y[rows].float() - ref).norm() / ref.norm()).item() <= 2e-3, s
