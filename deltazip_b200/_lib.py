@@ -83,6 +83,11 @@ _SIGNATURES = {
     "dz_grouped_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "dz_grouped_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_int64, c_void_p, c_size_t, c_void_p]),
+    "dz_quant_find_params": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "dz_sparsegpt_block": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "dz_pack_gptq": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                             c_void_p, c_void_p]),
     "dz_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "dz_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "dz_rotary_and_cache": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -264,6 +264,28 @@ int dz_paged_attention_decode(const void* qkv, int q_row_stride, void* out, cons
                               void* workspace, size_t workspace_bytes, int dtype, void* stream);
 
 /*
+ * Compression on the device (float32 in, the reference's arithmetic operation by operation).
+ *
+ * dz_quant_find_params: per-row symmetric grid of W [N, K]: scale[n], zero[n] = 2^(bits-1)
+ *   (Quantizer.find_params, deltazip/core/quant.py:48-86, per channel, symmetric).
+ * dz_sparsegpt_block: one block of <= 128 columns of SparseGPT.fasterprune with 2:4 pruning
+ *   (deltazip/core/sparsegpt.py:98-146): W_block points at column i1 of the current W (row
+ *   stride ldw), hinv_block at element (i1, i1) of the upper Cholesky factor of H^-1 (row stride
+ *   ldh).  Writes Q [N, count] (pruned + quantised block) and Err [N, count] ((w - q) / Hinv_ii)
+ *   and adds every row's loss to loss[n] (may be NULL).  The caller copies Q into W and applies
+ *   W[:, i2:] -= Err @ Hinv[i1:i2, i2:] before the next block.  count % 4 == 0.
+ * dz_pack_gptq: QuantLinear.pack (deltazip/nn_modules/qlinear.py:83-183, one group) of the
+ *   quantised W [N, K]: qweight int32 [K*bits/32, N], qzeros int32 [1, N*bits/32], scales fp16
+ *   [1, N] -- the tensors the reference stores and dz_convert_from_gptq reads.
+ */
+int dz_quant_find_params(const float* W, int N, int K, int bits, float* scale, float* zero, void* stream);
+int dz_sparsegpt_block(const float* W_block, int64_t ldw, const float* hinv_block, int64_t ldh,
+                       const float* scale, const float* zero, int bits, int N, int count, float* Q,
+                       float* Err, float* loss, void* stream);
+int dz_pack_gptq(const float* Wq, const float* scale, const float* zero, int N, int K, int bits,
+                 int32_t* qweight, int32_t* qzeros, uint16_t* scales, void* stream);
+
+/*
  * Delta swap-in: one asynchronous host->device copy of a delta's slot bytes
  * from PINNED host memory on `copy_stream`, preceded by a zero fill of the
  * destination when `zero_first` != 0 (the reference resets a slot before it

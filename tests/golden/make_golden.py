@@ -121,6 +121,59 @@ def reference_checkpoint(quant, qlinear, out_dir, bits, seed, hidden=256, inter=
     print(out_dir, {k: tuple(v.shape) for k, v in state.items() if k.endswith("qweight")})
 
 
+def _load_sparsegpt(ref):
+    """deltazip/core/sparsegpt.py uses relative imports: give it a stand-in parent package made of
+    the two sibling files it needs, all loaded by file path."""
+    import types
+    pkg = types.ModuleType("dz_ref_core")
+    pkg.__path__ = [os.path.join(ref, "deltazip/core")]
+    sys.modules["dz_ref_core"] = pkg
+    for name in ("quant", "sparsity_utils", "sparsegpt"):
+        spec = importlib.util.spec_from_file_location(f"dz_ref_core.{name}",
+                                                      os.path.join(ref, f"deltazip/core/{name}.py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[f"dz_ref_core.{name}"] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules["dz_ref_core.sparsegpt"], sys.modules["dz_ref_core.quant"]
+
+
+def sparsegpt_case(ref, out_path, n, k, bits, seed):
+    """SparseGPT.fasterprune (deltazip/core/sparsegpt.py:45-196) of the reference itself, on CPU,
+    with a Hessian accumulated by its add_batch from random calibration inputs, prunen:prunem =
+    2:4 and the symmetric per-row quantiser.  Stored: the delta, the upper Cholesky factor of the
+    damped H^-1 (recomputed here with the same torch calls fasterprune makes, on the same H), and
+    fasterprune's outputs.  The only change to the reference's behaviour is that its call of
+    torch.cuda.synchronize() is made a no-op (this machine has no GPU)."""
+    sparsegpt, quant = _load_sparsegpt(ref)
+    torch.cuda.synchronize = lambda *a, **kw: None
+    g = torch.Generator().manual_seed(seed)
+    delta = torch.randn(n, k, generator=g) * 1e-2
+    calib = torch.randn(96, k, generator=g) * (0.5 + torch.rand(k, generator=g))   # uneven column energy
+    layer = torch.nn.Linear(k, n, bias=False)
+    layer.weight.data = delta.clone()
+    sg = sparsegpt.SparseGPT(layer)
+    for i in range(0, 96, 32):
+        sg.add_batch(calib[i:i + 32], None)
+    H = sg.H.clone()
+    sg.quantizer = quant.Quantizer()
+    sg.quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+    scale, zero, g_idx, avg_loss, W = sg.fasterprune(0.5, prunen=2, prunem=4, blocksize=128, percdamp=0.01)
+    # the factor fasterprune derived from H (same calls, same machine)
+    Hd = H.clone()
+    dead = torch.diag(Hd) == 0
+    Hd[dead, dead] = 1
+    damp = 0.01 * torch.mean(torch.diag(Hd))
+    idx = torch.arange(k)
+    Hd[idx, idx] += damp
+    Hd = torch.linalg.cholesky(Hd)
+    Hd = torch.cholesky_inverse(Hd)
+    hinv = torch.linalg.cholesky(Hd, upper=True)
+    np.savez_compressed(out_path, bits=np.int32(bits), delta=delta.numpy(), H=H.numpy(), hinv=hinv.numpy(),
+                        wq=W.float().numpy(), scale=scale.flatten().numpy(), zero=zero.flatten().numpy(),
+                        avg_loss=np.float32(avg_loss), nsamples=np.int32(sg.nsamples))
+    print(out_path, "avg loss", avg_loss, "zeros", float((W == 0).float().mean()))
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path of a deltazip checkout>")
@@ -141,6 +194,8 @@ def main():
         assert bool(out["dense_is_fp16_exact"])
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
         print(name, {kk: getattr(v, "shape", None) for kk, v in out.items()})
+    sparsegpt_case(ref, os.path.join(HERE, "sparsegpt_b4_n32_k256.npz"), 32, 256, 4, seed=20)
+    sparsegpt_case(ref, os.path.join(HERE, "sparsegpt_b2_n32_k128.npz"), 32, 128, 2, seed=21)
     reference_checkpoint(quant, qlinear, os.path.join(HERE, "ref_ckpt_b4"), 4, seed=10)
     reference_checkpoint(quant, qlinear, os.path.join(HERE, "ref_ckpt_b2"), 2, seed=11)
 
