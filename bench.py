@@ -265,11 +265,26 @@ def run_ours(args):
             step_bytes += algorithmic_bytes(TOKENS, n, k, active, BITS)
 
     stage_ptr, stage_len = ctypes.c_void_p(), ctypes.c_size_t()
+    push = _lib.PushTarget()
+    fused = car is not None and args.fused_ar and car.can_push(TOKENS, HIDDEN, torch.float16)
 
     def launch(a, rowp, y, collectives=True):
         """One projection: the SBMM and, for a row-parallel layer under tensor parallelism, the
         all-reduce of its partial output.  Returns the number of this library's launches."""
         reduce = rowp and tp > 1 and collectives
+        if reduce and fused:
+            # fused: the SBMM's epilogue pushes finished tiles into every rank's receive slot and
+            # flags them; the reduction kernel only sums local memory
+            L.dz_allreduce_push_target(car._ctx, TOKENS, a.N, _lib.DZ_DTYPE_F16, ctypes.byref(push))
+            a.push = ctypes.pointer(push)
+            rc = L.dz_sbmm(ctypes.byref(a), stream)
+            a.push = None
+            if rc:
+                _lib.check(rc, "dz_sbmm")
+            rc = L.dz_allreduce_run_pushed(car._ctx, y.data_ptr(), TOKENS, a.N, _lib.DZ_DTYPE_F16, stream)
+            if rc:
+                _lib.check(rc, "dz_allreduce_run_pushed")
+            return 2
         if reduce and car is not None:
             # the SBMM writes its partial output straight into the staging buffer of the
             # all-reduce that follows (buffers alternate from call to call)
@@ -371,6 +386,11 @@ def run_ours(args):
             for name, n, k, rowp in projs:
                 e = entry[name]
                 reduce = rowp and tp > 1
+                if reduce and fused:
+                    ops.sbmm(xd[k], e["q"], e["s"], e["m"], seg, e["w"], bits=BITS, stable=True,
+                             push=car.push_target(TOKENS, n, torch.float16))
+                    y = car.all_reduce_pushed(TOKENS, n, torch.float16, out=y_dev[n])
+                    continue
                 out = car.staging_like((TOKENS, n), torch.float16) if (reduce and car) else y_dev[n]
                 y = ops.sbmm(xd[k], e["q"], e["s"], e["m"], seg, e["w"], out=out, bits=BITS, stable=True)
                 if reduce:
@@ -418,7 +438,9 @@ def run_ours(args):
                 "tokens": TOKENS, "deltas": NUM_DELTAS, "active_deltas": active, "bits": BITS,
                 "layers": args.layers, "sbmm_calls_per_step": n_calls,
                 "parallelism": f"tp{world}",
-                "allreduce": ("peer-memory (dz_allreduce_run, %s)" % (
+                "allreduce": ("fused: SBMM epilogue pushes tiles to every rank, local sum "
+                              "(dz_allreduce_run_pushed)" if fused else
+                              "peer-memory (dz_allreduce_run, %s)" % (
                                   {0: "one-shot kernel at this size", 1: "one-shot kernel (forced)",
                                    2: "two-stage kernel (forced)"}[args.ar_variant])
                               if car is not None
@@ -964,6 +986,9 @@ def main():
                          "profiling captures and smoke runs)")
     ap.add_argument("--allreduce", default="custom", choices=["custom", "nccl"],
                     help="N>1: all-reduce after the row-parallel layers (library peer-memory kernel or NCCL)")
+    ap.add_argument("--fused-ar", type=int, default=0, choices=[0, 1],
+                    help="N>1: 1 = row-parallel SBMM pushes its tiles to all ranks, 0 = separate all-reduce "
+                         "kernel fed from the staging buffer (default: measured faster)")
     ap.add_argument("--ar-variant", type=int, default=0, choices=[0, 1, 2],
                     help="peer-memory all-reduce kernel: 0 by size (default), 1 one-shot, 2 two-stage")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libdeltazip_b200.so")
@@ -34,6 +34,12 @@ DZ_SBMM_ACCUMULATE = 1
 DZ_SBMM_INPUTS_STABLE = 2
 
 
+class PushTarget(Structure):
+    """Mirror of dz_push_target."""
+    _fields_ = [("world", c_int32), ("rank", c_int32), ("epoch", c_uint32), ("reserved", c_uint32),
+                ("data", c_void_p * 8), ("flags", c_void_p * 8)]
+
+
 class SbmmArgs(Structure):
     """Mirror of dz_sbmm_args."""
     _fields_ = [
@@ -46,6 +52,7 @@ class SbmmArgs(Structure):
         ("tokens_sorted", c_int32), ("flags", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
         ("y_stride", c_int64),
+        ("push", POINTER(PushTarget)),
     ]
 
 
@@ -108,6 +115,8 @@ _SIGNATURES = {
     "dz_allreduce_run": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "dz_allreduce_status": (c_int, [c_void_p, POINTER(c_int)]),
     "dz_allreduce_set_variant": (c_int, [c_void_p, c_int]),
+    "dz_allreduce_push_target": (c_int, [c_void_p, c_int, c_int, c_int, POINTER(PushTarget)]),
+    "dz_allreduce_run_pushed": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "dz_allreduce_destroy": (c_int, [c_void_p]),
 }
 

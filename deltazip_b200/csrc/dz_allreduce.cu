@@ -25,6 +25,13 @@
 // parts of all peers.  Each rank then pulls 2 (world-1)/world of the message over NVLink
 // instead of (world-1) times the message.
 //
+// Third form, fused with the producer: the row-parallel SBMM does not write its partial output
+// to local memory at all -- its epilogue stores every finished output tile straight into a
+// receive slot (one per source rank) inside EVERY rank's region and then raises a per-tile flag
+// there (dz_allreduce_push_target hands the kernel the addresses).  The transfer rides under the
+// SBMM's own tail; the reduction (dz_allreduce_run_pushed) only waits for flags that are usually
+// set already and sums slots in local memory, in rank order.
+//
 // A wait that does not complete within the time limit records DZ_ERR_TIMEOUT in the region's
 // status word and the kernel returns without reducing; nothing spins forever.
 // No multicast objects are used, only ordinary peer loads and stores.
@@ -57,7 +64,10 @@ constexpr int kArThreads = 512;
 constexpr size_t kStatusOff = 0;                        // int status
 constexpr size_t kFlagsOff = 4096;                      // uint32 flag[kMaxWorld][kMaxBlocks]
 constexpr size_t kFlags2Off = 4096 + 2048;              // second table (two-stage kernel, stage B)
-constexpr size_t kStagingOff = 8192;
+constexpr size_t kPushFlagsOff = 8192;                  // uint32 flag[kMaxWorld][DZ_PUSH_MAX_FLAGS]
+constexpr size_t kStagingOff = 16384;
+constexpr size_t kPushSlotBytes = (size_t)2 << 20;      // receive slot per source rank and parity
+static_assert(kMaxWorld * DZ_PUSH_MAX_FLAGS * 4 <= kStagingOff - kPushFlagsOff, "push flag table");
 static_assert(kMaxWorld * kMaxBlocks * 4 <= 2048, "flag tables are 2 KB each");
 constexpr unsigned long long kArTimeoutNs = 1000ull * 1000 * 1000;
 
@@ -325,6 +335,91 @@ allreduce_twostage_kernel(const ArParams p) {
   }
 }
 
+// Reduction of tiles the producers pushed.  Block b handles output tile b (128 columns of every
+// row): it waits (bounded) until every source rank has raised the tile's flag for every token
+// block, then sums the `world` receive slots of the own region in rank order.
+struct PushedParams {
+  uint8_t* region;          // own region
+  void* out;
+  int M, N, world, parity, token_blocks, num_tiles;
+  unsigned epoch;
+  size_t push_off;          // byte offset of the receive slots inside the region
+};
+
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(256)
+allreduce_pushed_kernel(const PushedParams p) {
+  __shared__ int s_abort;
+  const int tile = blockIdx.x;
+  if (threadIdx.x == 0) s_abort = 0;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __syncthreads();
+  // one waiting thread per (source rank, token block)
+  for (int w = threadIdx.x; w < WORLD * p.token_blocks; w += 256) {
+    const int src = w / p.token_blocks, tb = w % p.token_blocks;
+    const unsigned* flag = reinterpret_cast<const unsigned*>(p.region + kPushFlagsOff) +
+                           src * DZ_PUSH_MAX_FLAGS + tb * p.num_tiles + tile;
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+      unsigned seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if ((int)(seen - p.epoch) >= 0) break;
+      if ((it & 255u) == 255u) {
+        const unsigned long long now = ar_globaltimer();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > kArTimeoutNs) {
+          s_abort = 1;
+          atomicCAS(reinterpret_cast<int*>(p.region + kStatusOff), 0, (int)DZ_ERR_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (s_abort) return;
+  const uint8_t* slots = p.region + p.push_off + (size_t)p.parity * WORLD * kPushSlotBytes;
+  constexpr int kVecPerTileRow = 128 / Vec<T>::kN;         // 16-byte vectors of one row of a tile
+  const int row_vec = p.N / Vec<T>::kN;
+  uint4* dst = reinterpret_cast<uint4*>(p.out);
+  for (int i = threadIdx.x; i < p.M * kVecPerTileRow; i += 256) {
+    const int row = i / kVecPerTileRow, v = i % kVecPerTileRow;
+    const size_t idx = (size_t)row * row_vec + (size_t)tile * kVecPerTileRow + v;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const uint4 x = __ldcg(reinterpret_cast<const uint4*>(slots + (size_t)r * kPushSlotBytes) + idx);
+      Vec<T>::add(acc, x);
+    }
+    dst[idx] = Vec<T>::pack(acc);
+  }
+}
+
+template <typename T>
+cudaError_t launch_pushed(const PushedParams& p, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.num_tiles);
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  switch (p.world) {
+    case 2: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 2>, p);
+    case 3: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 3>, p);
+    case 4: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 4>, p);
+    case 5: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 5>, p);
+    case 6: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 6>, p);
+    case 7: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 7>, p);
+    default: return cudaLaunchKernelEx(&cfg, allreduce_pushed_kernel<T, 8>, p);
+  }
+}
+
 template <typename T>
 cudaError_t launch_allreduce(const ArParams& p, int blocks, bool two_stage, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
@@ -366,7 +461,8 @@ using namespace dz;
 extern "C" {
 
 size_t dz_allreduce_region_bytes(size_t max_bytes) {
-  return kStagingOff + 2 * ((max_bytes + 255) & ~(size_t)255);
+  // header and flag tables, two staging buffers, then 2 (parity) x 8 receive slots
+  return kStagingOff + 2 * ((max_bytes + 255) & ~(size_t)255) + 2 * kMaxWorld * kPushSlotBytes;
 }
 
 int dz_allreduce_create(dz_allreduce_ctx** out, int rank, int world, size_t max_bytes) {
@@ -380,7 +476,7 @@ int dz_allreduce_create(dz_allreduce_ctx** out, int rank, int world, size_t max_
   c->region_bytes = dz_allreduce_region_bytes(max_bytes);
   if (cudaGetDevice(&c->device) != cudaSuccess ||
       cudaMalloc(reinterpret_cast<void**>(&c->region), c->region_bytes) != cudaSuccess ||
-      cudaMemset(c->region, 0, kStagingOff) != cudaSuccess) {
+      cudaMemset(c->region, 0, kStagingOff) != cudaSuccess) {   // status word and all flag tables
     if (c->region) cudaFree(c->region);
     delete c;
     return DZ_ERR_CUDA;
@@ -469,6 +565,48 @@ int dz_allreduce_run(dz_allreduce_ctx* c, const void* in, void* out, int64_t cou
   if (dtype == DZ_DTYPE_F16) DZ_CUDA_OK(launch_allreduce<__half>(p, blocks, two_stage, st));
   else if (dtype == DZ_DTYPE_BF16) DZ_CUDA_OK(launch_allreduce<__nv_bfloat16>(p, blocks, two_stage, st));
   else DZ_CUDA_OK(launch_allreduce<float>(p, blocks, two_stage, st));
+  return DZ_OK;
+}
+
+int dz_allreduce_push_target(dz_allreduce_ctx* c, int M, int N, int dtype, dz_push_target* t) {
+  if (!c || !t || !c->connected) return DZ_ERR_INVALID_ARG;
+  if (dtype != DZ_DTYPE_F16 && dtype != DZ_DTYPE_BF16) return DZ_ERR_UNSUPPORTED;
+  if (M <= 0 || N <= 0 || N % 128) return DZ_ERR_SHAPE;
+  const int tbs = (M + 127) / 128;
+  if ((size_t)M * N * 2 > kPushSlotBytes || tbs * (N / 128) > DZ_PUSH_MAX_FLAGS) return DZ_ERR_TOO_LARGE;
+  const size_t push_off = kStagingOff + 2 * c->max_bytes;
+  const unsigned parity = c->epoch & 1u;
+  memset(t, 0, sizeof(*t));
+  t->world = c->world;
+  t->rank = c->rank;
+  t->epoch = c->epoch + 1;
+  for (int r = 0; r < c->world; ++r) {
+    // this rank's receive slot and flag row inside rank r's region
+    t->data[r] = c->peers[r] + push_off + ((size_t)parity * c->world + c->rank) * kPushSlotBytes;
+    t->flags[r] = c->peers[r] + kPushFlagsOff + (size_t)c->rank * DZ_PUSH_MAX_FLAGS * 4;
+  }
+  return DZ_OK;
+}
+
+int dz_allreduce_run_pushed(dz_allreduce_ctx* c, void* out, int M, int N, int dtype, void* stream) {
+  if (!c || !out || !c->connected) return DZ_ERR_INVALID_ARG;
+  if (dtype != DZ_DTYPE_F16 && dtype != DZ_DTYPE_BF16) return DZ_ERR_UNSUPPORTED;
+  if (M <= 0 || N <= 0 || N % 128) return DZ_ERR_SHAPE;
+  const int tbs = (M + 127) / 128;
+  if ((size_t)M * N * 2 > kPushSlotBytes || tbs * (N / 128) > DZ_PUSH_MAX_FLAGS) return DZ_ERR_TOO_LARGE;
+  if ((uintptr_t)out & 15) return DZ_ERR_ALIGNMENT;
+  PushedParams p;
+  p.region = c->region;
+  p.out = out;
+  p.M = M; p.N = N; p.world = c->world;
+  p.parity = (int)(c->epoch & 1u);
+  p.token_blocks = tbs;
+  p.num_tiles = N / 128;
+  p.epoch = ++c->epoch;
+  p.push_off = kStagingOff + 2 * c->max_bytes;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == DZ_DTYPE_F16) DZ_CUDA_OK(launch_pushed<__half>(p, st));
+  else DZ_CUDA_OK(launch_pushed<__nv_bfloat16>(p, st));
   return DZ_OK;
 }
 

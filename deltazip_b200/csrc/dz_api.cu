@@ -36,11 +36,18 @@ int check_sbmm_args(const dz_sbmm_args* a, bool base_only, bool check_workspace)
   if (a->M < 0) return DZ_ERR_INVALID_ARG;
   if (a->M == 0) return DZ_OK;  // nothing to do; pointers may be null
   // w_base may be absent for dz_sbmm: only the delta products are then computed
-  if (!a->x || !a->y || (base_only && !a->w_base)) return DZ_ERR_INVALID_ARG;
+  if (!a->x || (!a->y && !a->push) || (base_only && !a->w_base)) return DZ_ERR_INVALID_ARG;
+  if (a->push) {
+    if (a->push->world < 2 || a->push->world > 8 || (a->flags & DZ_SBMM_ACCUMULATE))
+      return DZ_ERR_INVALID_ARG;
+    if ((size_t)((a->M + 127) / 128) * (size_t)(a->N / 128) > DZ_PUSH_MAX_FLAGS) return DZ_ERR_TOO_LARGE;
+    for (int r = 0; r < a->push->world; ++r)
+      if (!a->push->data[r] || !a->push->flags[r]) return DZ_ERR_INVALID_ARG;
+  }
   int rc = check_shape(a->N, a->K, base_only ? 4 : a->bits);
   if (rc) return rc;
   if (a->dtype != DZ_DTYPE_F16 && a->dtype != DZ_DTYPE_BF16) return DZ_ERR_INVALID_ARG;
-  if (!aligned16(a->x) || !aligned16(a->w_base) || !aligned16(a->y)) return DZ_ERR_ALIGNMENT;
+  if (!aligned16(a->x) || !aligned16(a->w_base) || (!a->push && !aligned16(a->y))) return DZ_ERR_ALIGNMENT;
   if (!base_only) {
     if (!a->qweight || !a->meta || !a->scales || !a->segments) return DZ_ERR_INVALID_ARG;
     if (a->num_slots <= 0 || a->num_slots > kMaxSlots) return DZ_ERR_INVALID_ARG;
@@ -156,7 +163,7 @@ int dz_sbmm_simt(const dz_sbmm_args* args, void* stream) {
   int rc = check_sbmm_args(args, false, true);
   if (rc || args->M == 0) return rc;
   if (args->dtype != DZ_DTYPE_F16) return DZ_ERR_UNSUPPORTED;   // the twin is fp16 only
-  if ((args->flags & DZ_SBMM_ACCUMULATE) || (args->y_stride && args->y_stride != args->N) || !args->w_base)
+  if (args->push || (args->flags & DZ_SBMM_ACCUMULATE) || (args->y_stride && args->y_stride != args->N) || !args->w_base)
     return DZ_ERR_UNSUPPORTED;                                   // plain y = base + delta only
   return launch_sbmm_simt(*args, false, (cudaStream_t)stream);
 }

@@ -136,6 +136,11 @@ struct Params {
   float* partials;
   int* counters;
   int* status;
+  // fused all-reduce: finished tiles go to every rank's receive slot, then a flag per tile
+  int push_world;
+  unsigned push_epoch;
+  void* push_data[8];
+  unsigned* push_flags[8];
 };
 
 // The pair (code_lo - zero, code_hi - zero) as fp16 (DT = 0) or bf16 (DT = 1) from the
@@ -926,8 +931,13 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const int prow = p.row0 + col + i;
               if (prow < p.M) {
                 const int tok = perm ? perm[prow] : prow;
-                store_out<DT>(p.y, (size_t)tok * (size_t)p.ldy + n0 + r, __uint_as_float(v[i]),
-                              p.accumulate);
+                const size_t at = (size_t)tok * (size_t)p.ldy + n0 + r;
+                if (p.push_world == 0) {
+                  store_out<DT>(p.y, at, __uint_as_float(v[i]), p.accumulate);
+                } else {
+                  for (int pr = 0; pr < p.push_world; ++pr)
+                    store_out<DT>(p.push_data[pr], at, __uint_as_float(v[i]), 0);
+                }
               }
             }
           } else {
@@ -951,6 +961,18 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (ep_tid == 0)
           asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.counters + 2 * tile + 1)
                        : "memory");
+      } else if (p.push_world != 0) {
+        // the tile is complete in every rank's receive slot once all epilogue threads' stores
+        // are ordered before the flags (same pattern, system scope: the readers are other GPUs)
+        named_bar_sync(1, 128 * kNumWG);
+        if (ep_tid == 0) {
+          __threadfence_system();
+          for (int pr = 0; pr < p.push_world; ++pr)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
+                             p.push_flags[pr] + p.token_block * p.num_tiles + tile),
+                         "r"(p.push_epoch)
+                         : "memory");
+        }
       }
       cta_first_fragment = false;
       u += ku1 - ku0;
@@ -1053,9 +1075,19 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.num_tiles = a.N / kTileN;
   p.base_only = base_only ? 1 : 0;
   p.delta_only = (!base_only && a.w_base == nullptr) ? 1 : 0;
+  p.push_world = 0;
+  p.push_epoch = 0;
+  if (a.push) {
+    p.push_world = a.push->world;
+    p.push_epoch = a.push->epoch;
+    for (int r = 0; r < 8; ++r) {
+      p.push_data[r] = a.push->data[r];
+      p.push_flags[r] = reinterpret_cast<unsigned*>(a.push->flags[r]);
+    }
+  }
   p.accumulate = (a.flags & DZ_SBMM_ACCUMULATE) ? 1 : 0;
   p.stable = (a.flags & DZ_SBMM_INPUTS_STABLE) ? 1 : 0;
-  p.ldy = a.y_stride ? a.y_stride : a.N;
+  p.ldy = (a.y_stride && !a.push) ? a.y_stride : a.N;
   p.tokens_sorted = sorted ? 1 : 0;
   p.epi_units = kEpilogueUnits;
   p.total_units = p.num_tiles * (p.num_kunits + p.epi_units);

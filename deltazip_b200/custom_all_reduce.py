@@ -79,6 +79,32 @@ class CustomAllreduce:
                                      _DTYPES[inp.dtype], stream), "dz_allreduce_run")
         return out
 
+    # -- fused form: the producer pushes its tiles, the reduction sums local slots ------------
+    PUSH_SLOT_BYTES = 2 << 20
+
+    def can_push(self, rows: int, cols: int, dtype: torch.dtype) -> bool:
+        """Whether an [rows, cols] partial output of `dtype` can take the fused path."""
+        return (self.world_size > 1 and dtype in (torch.float16, torch.bfloat16) and cols % 128 == 0
+                and 0 < rows * cols * 2 <= self.PUSH_SLOT_BYTES
+                and ((rows + 127) // 128) * (cols // 128) <= 256)
+
+    def push_target(self, rows: int, cols: int, dtype: torch.dtype) -> "_lib.PushTarget":
+        """Addresses for the producer of the NEXT reduction (pass as `push=` to ops.sbmm, then
+        call all_reduce_pushed with the same shape)."""
+        t = _lib.PushTarget()
+        check(lib().dz_allreduce_push_target(self._ctx, rows, cols, _DTYPES[dtype], ctypes.byref(t)),
+              "dz_allreduce_push_target")
+        return t
+
+    def all_reduce_pushed(self, rows: int, cols: int, dtype: torch.dtype,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((rows, cols), dtype=dtype, device=self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        check(lib().dz_allreduce_run_pushed(self._ctx, out.data_ptr(), rows, cols, _DTYPES[dtype], stream),
+              "dz_allreduce_run_pushed")
+        return out
+
     def set_variant(self, variant: int) -> None:
         """0: kernel chosen by message size and rank count; 1: always the one-shot kernel;
         2: the two-stage kernel whenever there are more than two ranks (all ranks alike)."""

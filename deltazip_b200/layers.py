@@ -286,6 +286,12 @@ class MergedQKVParallelLinearWithDelta(ColumnParallelLinearWithDelta):
 
 
 class RowParallelLinearWithDelta(BaseLayerWithDelta):
+    # True: the SBMM epilogue pushes finished tiles into every rank's receive slot and the
+    # reduction sums local memory.  Off by default: measured on 2 and 4 B200s the W-fold 2-byte
+    # remote stores lengthen the kernel's tail by more than the pull they replace (N=4: 5.08 ms
+    # per step against 4.47 ms with the separate one-shot kernel).
+    FUSED_ALL_REDUCE = False
+
     def forward(self, input_):
         base = self.base_layer
         if base.input_is_parallel:
@@ -293,21 +299,29 @@ class RowParallelLinearWithDelta(BaseLayerWithDelta):
         else:
             x = input_[..., base.shard[0]:base.shard[1]].contiguous()
         reduce = base.reduce_results and base.tp_size > 1
+        if not reduce:
+            return self.apply_weights(x), None
+        handle = get_custom_ar_handle()
+        rows = x.numel() // x.shape[-1]
+        n = base.linear_weights["weight"].shape[0]
+        if handle is not None and self.FUSED_ALL_REDUCE and self.segments is not None and rows > 0 \
+                and handle.can_push(rows, n, x.dtype):
+            # fused: the kernel's epilogue stores every finished tile into all ranks' receive
+            # slots and flags it; the reduction only sums local memory
+            target = handle.push_target(rows, n, x.dtype)
+            ops.sbmm(x, self.qweight_stacked, self.scales_stacked, self.meta_stacked, self.segments,
+                     base.linear_weights["weight"], bits=self.bits, stable=True, push=target)
+            out = handle.all_reduce_pushed(rows, n, x.dtype)
+            return out.reshape(*x.shape[:-1], n), None
         staged = None
-        if reduce:
+        nbytes = rows * n * x.element_size()
+        if handle is not None and 0 < nbytes <= handle.max_size and nbytes % 16 == 0:
             # produce the partial output directly in peer-visible memory when the
             # peer-memory all-reduce will take it (saves its copy-in)
-            handle = get_custom_ar_handle()
-            rows = x.numel() // x.shape[-1]
-            n = base.linear_weights["weight"].shape[0]
-            if handle is not None and 0 < rows * n * x.element_size() <= handle.max_size and \
-                    (rows * n * x.element_size()) % 16 == 0:
-                staged = handle.staging_like((rows, n), x.dtype)
+            staged = handle.staging_like((rows, n), x.dtype)
         out = self.apply_weights(x, out=staged)
-        if reduce:
-            out = tensor_model_parallel_all_reduce(out)
-            out = out.reshape(*x.shape[:-1], out.shape[-1])
-        return out, None
+        out = tensor_model_parallel_all_reduce(out)
+        return out.reshape(*x.shape[:-1], out.shape[-1]), None
 
     @classmethod
     def can_replace_layer(cls, source_layer, delta_config, packed_modules_list, model_config=None):

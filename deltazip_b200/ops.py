@@ -184,7 +184,8 @@ def _bits_from_shapes(qweight_stacked: torch.Tensor, k: int) -> int:
 def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.Tensor,
          meta_stacked: torch.Tensor, segments: Segments, base_weight: Optional[torch.Tensor],
          out: Optional[torch.Tensor] = None, bits: Optional[int] = None,
-         _entry: str = "dz_sbmm", accumulate: bool = False, stable: bool = False) -> torch.Tensor:
+         _entry: str = "dz_sbmm", accumulate: bool = False, stable: bool = False,
+         push=None) -> Optional[torch.Tensor]:
     """y = x W^T + x dequant(delta_slot(i))^T with a prebuilt segment table.  With
     `base_weight=None` only the delta products are computed (rows of slot -1 get 0).
     `out` may be a column slice [:, a:a+N] of a wider row-major tensor; with
@@ -192,7 +193,10 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
     caller's statement that the base weight, the slot stacks and the segment table were not
     written by the operation right before this call on the stream (DZ_SBMM_INPUTS_STABLE): the
     kernel then starts loading them while its predecessor finishes.  After writing any of them
-    with a torch op, call `stream_fence()` before relying on it."""
+    with a torch op, call `stream_fence()` before relying on it.  With `push` (a target from
+    CustomAllreduce.push_target) the output is not written locally at all: every finished tile
+    goes to all tensor-parallel ranks' receive slots and `all_reduce_pushed` yields the sum;
+    the call then returns None."""
     _need_cuda(x, qweight_stacked, scales_stacked, meta_stacked)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
@@ -209,6 +213,24 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
         raise ValueError(f"segment table was built for {segments.m} tokens, x has {m}")
     if bits is None:
         bits = _bits_from_shapes(qweight_stacked, k)
+    if push is not None:
+        if accumulate or out is not None or m == 0:
+            raise ValueError("a pushed output takes neither `out` nor `accumulate`, and needs rows")
+        nbytes = lib().dz_sbmm_workspace_bytes(m, n, k, int(segments.sorted))
+        ws = _workspace(x.device, nbytes)
+        args = SbmmArgs(
+            x=x2.data_ptr(), w_base=base_weight.data_ptr() if base_weight is not None else None,
+            qweight=qweight_stacked.data_ptr(), meta=meta_stacked.data_ptr(),
+            scales=scales_stacked.data_ptr(), qweight_stride=qweight_stacked.stride(0) * 4,
+            meta_stride=meta_stacked.stride(0) * 2, scales_stride=scales_stacked.stride(0) * 2,
+            segments=segments.buf.data_ptr(), y=None, M=m, N=n, K=k,
+            num_slots=qweight_stacked.shape[0], bits=bits, dtype=_dtype_code(x),
+            tokens_sorted=int(segments.sorted),
+            flags=_lib.DZ_SBMM_INPUTS_STABLE if stable else 0,
+            workspace=ws.data_ptr(), workspace_bytes=ws.numel(), y_stride=0,
+            push=ctypes.pointer(push))
+        check(getattr(lib(), _entry)(ctypes.byref(args), _stream()), _entry)
+        return None
     if out is None:
         if accumulate:
             raise ValueError("accumulate=True needs the tensor to add to (out)")

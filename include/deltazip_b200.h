@@ -105,6 +105,17 @@ int dz_build_segments(const void* indices, int index_dtype, int M, int num_slots
  * indices, base_weight), and the separate base GEMM
  * (serving/vllm/model_executor/layers/linear.py:85-96).
  */
+/* Where a row-parallel SBMM sends its partial output when it is fused with the all-reduce
+ * that follows (filled by dz_allreduce_push_target, see there). */
+#define DZ_PUSH_MAX_FLAGS 256
+typedef struct {
+  int32_t world, rank;
+  uint32_t epoch;           /* value the per-tile flags are raised to                  */
+  uint32_t reserved;
+  void* data[8];            /* rank r's receive slot for this rank's [M, N] partial     */
+  void* flags[8];           /* rank r's flag row for this rank (uint32 per tile)        */
+} dz_push_target;
+
 typedef struct {
   const void* x;            /* [M, K] row-major, 16-byte aligned                 */
   const void* w_base;       /* [N, K] row-major, 16-byte aligned; NULL for dz_sbmm:
@@ -143,6 +154,13 @@ typedef struct {
                                [0, N) of a wider output, i.e. one slice of a
                                merged layer (add_delta_slice,
                                serving/vllm/delta/deltazip.py:41-78)             */
+  const dz_push_target* push; /* host pointer or NULL.  Non-NULL (row-parallel layer under
+                               tensor parallelism): instead of writing y, the epilogue
+                               stores every finished output tile into the receive slot
+                               of every rank and raises the tile's flag there;
+                               dz_allreduce_run_pushed then produces the reduced
+                               [M, N].  y and y_stride are ignored, DZ_SBMM_ACCUMULATE
+                               is not allowed                                      */
 } dz_sbmm_args;
 
 /* flags of dz_sbmm_args */
@@ -329,6 +347,18 @@ int dz_allreduce_staging(dz_allreduce_ctx* ctx, void** ptr, size_t* bytes);
 int dz_allreduce_run(dz_allreduce_ctx* ctx, const void* in, void* out, int64_t count,
                      int dtype, void* stream);
 int dz_allreduce_status(dz_allreduce_ctx* ctx, int* status);
+/*
+ * Fused form (producer pushes, consumer sums locally).  For the NEXT reduction of an [M, N]
+ * tensor of `dtype` (N % 128 == 0, M*N*2 <= 2 MB): push_target fills the addresses a dz_sbmm
+ * call takes in args->push; after that call (the calls of all its token blocks are one call),
+ * run_pushed enqueues the kernel that waits for every rank's tiles and writes the sum to `out`
+ * (fp32 accumulation in rank order, bit-identical on all ranks).  push_target -> dz_sbmm ->
+ * run_pushed must follow each other on one stream, and every rank must issue the same sequence
+ * of reductions of either kind.  The role the reference gives to an all-reduce call after the
+ * row-parallel layer (serving/vllm/delta/layers_marlin.py:583-584).
+ */
+int dz_allreduce_push_target(dz_allreduce_ctx* ctx, int M, int N, int dtype, dz_push_target* target);
+int dz_allreduce_run_pushed(dz_allreduce_ctx* ctx, void* out, int M, int N, int dtype, void* stream);
 /* Kernel choice of later runs: 0 = by message size and rank count (one kernel that sums whole
  * slices for small messages, a reduce-scatter + all-gather kernel above the sizes at which
  * serving/csrc/custom_all_reduce.cuh:443-456 switches), 1 = always the former, 2 = the latter

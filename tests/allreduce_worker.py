@@ -27,6 +27,15 @@ def expected_sum(parts, dtype):
     return acc.to(dtype)
 
 
+def layer_sep_call(layer, xs):
+    """The layer's output through the separate (non-fused) all-reduce."""
+    layers.RowParallelLinearWithDelta.FUSED_ALL_REDUCE = False
+    try:
+        return layer(xs)[0].clone()
+    finally:
+        layers.RowParallelLinearWithDelta.FUSED_ALL_REDUCE = True      # the caller is in its fused loop
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -101,6 +110,30 @@ def main():
     rel = ((y_tp - ref).norm() / ref.norm()).item()
     assert rel < 1e-2, rel
     assert h.status() == 0
+
+    # --- fused form: the SBMM epilogue pushes its tiles to every rank, the reduction sums local
+    #     slots; same rounding as the separate all-reduce, so the outputs are bit-identical ---
+    for m2, sort in ((48, True), (300, True), (77, False)):
+        x2 = torch.randn(m2, k, generator=gen, device=dev).half()
+        idx2 = torch.randint(-1, slots, (m2,), generator=gen, device=dev)
+        if sort:
+            idx2 = torch.sort(idx2)[0]
+        seg = ops.Segments(m2, slots, dev).build(idx2, sorted_hint=sort)
+        layer.set_mapping(idx2, None, None, None, [m2], segments=seg)
+        xs = x2[:, lo:hi].contiguous()
+        layers.RowParallelLinearWithDelta.FUSED_ALL_REDUCE = False
+        y_sep = layer(xs)[0].clone()
+        layers.RowParallelLinearWithDelta.FUSED_ALL_REDUCE = True
+        for rep in range(6):                      # repeated: slots and flags alternate correctly
+            y_fused = layer(xs)[0]
+            assert torch.equal(y_fused, y_sep), (m2, sort, rep, (y_fused.float() - y_sep.float()).abs().max())
+            if rep % 2:                           # interleave with reductions of the other kind
+                assert torch.equal(layer_sep_call(layer, xs), y_sep)
+        ref2 = ops.apply_delta(x2, full[0], full[2], full[1], idx2, w).float()
+        assert ((y_fused.float() - ref2).norm() / ref2.norm()).item() < 1e-2
+    layers.RowParallelLinearWithDelta.FUSED_ALL_REDUCE = False
+    torch.cuda.synchronize()
+    assert h.status() == 0 and ops.read_status(dev) == 0
 
     # --- bounded wait: rank 0 issues a call nobody joins ---
     dist.barrier()

@@ -9,7 +9,9 @@ import pytest
 
 from oracle import deltazip_oracle as O
 
-CASES = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+# the pack / unpack / forward cases (the sparsegpt_* files hold the compressor's golden vectors and
+# are read by tests/test_gpu_compress.py and test_sparsegpt_restatement below)
+CASES = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "b[0-9]*.npz")))
 
 
 @pytest.fixture(params=CASES, ids=[os.path.basename(c)[:-4] for c in CASES])
@@ -125,3 +127,18 @@ def test_staged_reference_code_agrees_with_the_restatements():
         assert orc.rel_l2(y.numpy(), y2.numpy()) <= 1e-3
         dense_t = R.unpack_dense_t(layers[0])
         assert (dense_t.t().numpy().view(np.uint16) == orc.unpack(*deltas[0]).view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("name", ["sparsegpt_b2_n32_k128", "sparsegpt_b4_n32_k256"])
+def test_sparsegpt_golden_is_consistent_with_the_oracle_pieces(name, golden_dir):
+    """The compressor's golden vectors (the reference's fasterprune): the grid stored there is the
+    oracle's grid of the delta, every value lies on that grid, and every group of four keeps at
+    most two non-zero entries."""
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    bits = int(g["bits"])
+    scale, zero, maxq = O.find_params_sym(g["delta"], bits)
+    np.testing.assert_array_equal(scale, g["scale"])
+    np.testing.assert_array_equal(zero, g["zero"])
+    codes = g["wq"] / scale[:, None] + zero[:, None]
+    assert np.abs(codes - np.rint(codes)).max() < 1e-3 and codes.min() > -0.5 and codes.max() < maxq + 0.5
+    assert ((g["wq"] != 0).reshape(g["wq"].shape[0], -1, 4).sum(-1) <= 2).all()
