@@ -13,7 +13,9 @@ step streams them from HBM.  Data are seeded and synthetic.
 
 --config 3 / 4: full-model decode through deltazip_b200/engine.py: Llama-2-7B with 32 resident
 2-bit deltas and 128 sequences; Llama-2-13B with 64 2-bit deltas, 256 sequences and a Zipf(1.5)
-request-to-delta map, tensor parallel.
+request-to-delta map, tensor parallel.  --config 5: Llama-2-70B, 16 4-bit deltas in pinned host
+memory, 4 GPU slots, bursty arrivals, swap-in overlapped with decode (--duration seconds of
+arrivals on a virtual clock).
 
 N > 1: tensor parallel over N ranks (column-parallel qkv / gate_up, row-parallel o / down
 followed by the library's peer-memory all-reduce), shards cut at whole 128-wide units; the total
@@ -973,6 +975,199 @@ def run_decode_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------
+# Config 5: arrivals over time, deltas in pinned host memory, swap-in overlapped with decode
+# ---------------------------------------------------------------------------
+
+def run_swap(args):
+    """Llama-2-70B geometry, 16 4-bit deltas in pinned host memory, at most 4 resident on the
+    GPU, gamma-burst arrivals (mean 8 requests/s, CV 3), prompts U[128, 1024], outputs
+    U[64, 512], tensor parallel over all ranks.  The serving loop runs on a virtual clock that
+    advances by the measured duration of every iteration (prefill + one decode step), so a run
+    does not have to last as long as the arrival window; every rank takes the same decisions
+    (durations and upload completions are agreed through one small all-reduce per iteration)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from deltazip_b200 import ops, parallel_state, synth
+    from deltazip_b200.config import DeltaConfig
+    from deltazip_b200.engine import DecodeEngine, Sequence
+    from deltazip_b200.llama import LLAMA2_70B, LlamaConfig
+    from deltazip_b200.models import DeltaModel
+
+    world, rank, local_rank = dist_env()
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        parallel_state.initialize_model_parallel(world, disable_custom_all_reduce=(args.allreduce == "nccl"))
+    base = LLAMA2_70B
+    layers = args.layers or base.num_hidden_layers
+    cfg = LlamaConfig(base.hidden_size, base.intermediate_size, layers, base.num_attention_heads,
+                      base.num_key_value_heads, base.vocab_size)
+    bits, num_deltas, slots, max_seqs = 4, 16, 4, 64
+    duration = args.duration or 300.0
+    rate, cv = 8.0, 3.0
+
+    # ---- requests (same on every rank) ----
+    rng = np.random.default_rng(0)
+    shape = 1.0 / cv ** 2
+    gaps = rng.gamma(shape, (1.0 / rate) / shape, size=int(duration * rate * 3) + 16)
+    arrivals = np.cumsum(gaps)
+    arrivals = arrivals[arrivals < duration]
+    reqs = [dict(t=float(t), delta=int(rng.integers(1, num_deltas + 1)), prompt=int(rng.integers(128, 1025)),
+                 out=int(rng.integers(64, 513))) for t in arrivals]
+
+    kv_blocks = max_seqs * ((1024 + 512 + 15) // 16)
+    engine = DecodeEngine(cfg, DeltaConfig(max_deltas=slots, max_bitwidth=bits, max_cpu_deltas=num_deltas),
+                          max_seqs=max_seqs, kv_blocks=kv_blocks, device=device)
+    engine.attn_splits = 8 if engine.model.kv_heads * max_seqs < 256 else 1
+    mgr = engine.manager
+    arena_bytes = mgr.layout.total
+    # ---- host memory: how many distinct deltas can be pinned ----
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = 64 << 30
+    local_world = max(1, world)
+    fit = int(0.35 * avail / local_world // max(arena_bytes, 1))
+    host_deltas = max(2, min(num_deltas, fit))           # never pin more than a third of the free RAM
+    if world > 1:
+        t = torch.tensor([host_deltas], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        host_deltas = int(t.item())
+    if host_deltas <= slots:
+        raise SystemExit(f"host memory holds only {host_deltas} deltas of {arena_bytes >> 20} MiB per rank: "
+                         "nothing would ever be swapped; use fewer layers or more ranks")
+    # distinct synthetic data per delta for the first layer, copied to the other layers, written
+    # into GPU slot 0 as a staging area and read back into the delta's pinned arena
+    first = {}
+    for name, module in mgr.modules.items():
+        first.setdefault(name.rsplit(".", 1)[1], module)
+    for d in range(1, host_deltas + 1):
+        gen = torch.Generator(device=device).manual_seed(1000 * d + rank)
+        for leaf, module in first.items():
+            n, k = module.weight.shape
+            qw, qz, sc = synth.compress_delta_gptq(torch.randn((n, k), generator=gen, device=device) * 1e-3, bits)
+            ops.convert_from_gptq(qw, qz, sc, bits, check_status=(d == 1),
+                                  out=(module.qweight_stacked[0], module.meta_stacked[0], module.scales_stacked[0]))
+        for name, module in mgr.modules.items():
+            src = first[name.rsplit(".", 1)[1]]
+            if module is not src:
+                module.qweight_stacked[0].copy_(src.qweight_stacked[0])
+                module.meta_stacked[0].copy_(src.meta_stacked[0])
+                module.scales_stacked[0].copy_(src.scales_stacked[0])
+        dm = DeltaModel(d, bits, {})
+        dm.arena = torch.empty(arena_bytes, dtype=torch.uint8).pin_memory()
+        dm.arena.copy_(mgr.arena[0])
+        dm._arena_layout = mgr.layout
+        mgr.add_delta(dm)
+    mgr.arena[0].zero_()
+    torch.cuda.synchronize()
+
+    pending = [Sequence(i, (r["delta"] - 1) % host_deltas + 1, r["prompt"], r["out"], arrival=r["t"],
+                        prompt=torch.randint(0, cfg.vocab_size, (r["prompt"],),
+                                             generator=torch.Generator().manual_seed(i)))
+               for i, r in enumerate(reqs)]
+    waiting, done = [], []
+    now, iters, tokens_out, busy_with_upload = 0.0, 0, 0, 0
+    agree = torch.zeros(1 + num_deltas + 1, device=device, dtype=torch.float64)
+
+    def ready_all_ranks():
+        """For every delta being uploaded: has the upload finished on ALL ranks?"""
+        flags = {}
+        vec = torch.zeros(num_deltas + 1, dtype=torch.float64)
+        for d, idx in mgr._loading.items():
+            vec[d] = 0.0 if mgr._slot_ready[idx].query() else 1.0      # 1 = some rank still loading
+        if world > 1:
+            t = vec.to(device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            vec = t.cpu()
+        for d in mgr._loading:
+            flags[d] = vec[d].item() == 0.0
+        return flags
+
+    uploads0 = mgr.uploads
+    t_start = time.perf_counter()
+    while pending or waiting or engine.running:
+        while pending and pending[0].arrival <= now:
+            waiting.append(pending.pop(0))
+        if not waiting and not engine.running:
+            now = pending[0].arrival
+            continue
+        t0 = time.perf_counter()
+        flags = ready_all_ranks() if mgr._loading else {}
+        admitted = engine.admit_overlapped(waiting, ready=lambda d: flags.get(d, False))
+        group, group_tokens = [], 0
+        for s_ in admitted:                      # prompts run in passes of at most 2048 tokens
+            n_tok = int(s_.prompt.numel())
+            if group and group_tokens + n_tok > 2048:
+                engine.prefill(group)
+                group, group_tokens = [], 0
+            group.append(s_)
+            group_tokens += n_tok
+        if group:
+            engine.prefill(group)
+        if mgr._loading:
+            busy_with_upload += 1
+        if engine.running:
+            engine.decode_step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            agree[0] = dt
+            dist.all_reduce(agree[:1], op=dist.ReduceOp.MAX)
+            dt = agree[0].item()
+        now += dt
+        iters += 1
+        for s_ in list(engine.running):
+            if s_.first_token_time is None:
+                s_.first_token_time = now
+            if s_.generated >= s_.max_new:
+                tokens_out += s_.generated
+                done.append((s_.arrival, s_.first_token_time, now, s_.generated))
+                engine.retire(s_)
+        if not engine.running and not waiting and mgr._loading:
+            torch.cuda.synchronize()
+        if time.perf_counter() - t_start > (args.wall_limit or 600):
+            break
+    wall = time.perf_counter() - t_start
+    status = ops.read_status(device)
+    if rank == 0:
+        ttft = sorted(f - a for a, f, _, _ in done) or [0.0]
+        lat = sorted(e - a for a, _, e, _ in done) or [0.0]
+        line = {
+            "metric": "decode_tokens_per_s", "value": tokens_out / max(now, 1e-9), "unit": UNIT,
+            "n_gpus": world, "steps": iters, "warmup": 0, "ms_per_step": now / max(iters, 1) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {
+                "workload": "configs[4]: Llama-2-70B architecture (80 layers, hidden 8192, 64 q / 8 kv heads, "
+                            "inter 28672), 16 deltas 4-bit 2:4 in pinned host memory, at most 4 GPU-resident, "
+                            "gamma-burst arrivals (8 req/s, CV 3), prompt U[128,1024], output U[64,512], "
+                            "swap-in overlapped with decode; virtual clock advanced by measured iteration times",
+                "layers": layers, "parallelism": f"tp{world}", "arrival_window_s": duration,
+                "requests": len(reqs), "requests_finished": len(done), "max_concurrent_sequences": max_seqs,
+                "deltas": num_deltas, "deltas_in_host_memory": host_deltas, "gpu_slots": slots,
+                "delta_bytes_per_rank": arena_bytes, "swap_ins": engine.swap_ins,
+                "iterations_with_an_upload_in_flight": busy_with_upload,
+                "mean_ttft_s": sum(ttft) / len(ttft), "p90_ttft_s": ttft[int(0.9 * (len(ttft) - 1))],
+                "mean_latency_s": sum(lat) / len(lat), "makespan_s": now, "wall_s": wall,
+            },
+            "e2e": {"value": tokens_out / max(now, 1e-9), "unit": UNIT,
+                    "h2d_bytes_per_step": int((mgr.uploads - uploads0) * arena_bytes / max(iters, 1)),
+                    "d2h_bytes_per_step": 0, "note": "the whole loop is host-driven; value is the same measurement"},
+            "gpu_launches": iters * (layers * 10 + 3), "kernel_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        parallel_state.destroy_model_parallel()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -994,6 +1189,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")
     ap.add_argument("--duration", type=float, default=None,
                     help="config 5: seconds of simulated arrivals (default 300)")
+    ap.add_argument("--wall-limit", type=float, default=None,
+                    help="config 5: stop the serving loop after this many wall-clock seconds (default 600)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -1004,7 +1201,13 @@ def main():
             run_decode(args)
         return
     if args.config == 5:
-        raise SystemExit("config 5 is not built in this version")
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's serving engine needs ray, "
+                              "xformers and cupy, none of which is installed; its CPU path for the SBMM is "
+                              "timed by --config 2/3/4"}), flush=True)
+        else:
+            run_swap(args)
+        return
     if args.layers is None:
         args.layers = LAYERS
     if args.impl == "reference":

@@ -50,6 +50,7 @@ class DecodeEngine:
         self.positions = None
         self.block_tables = None
         self.attn_splits = 1
+        self.swap_ins = 0
 
     # -- batch composition -----------------------------------------------------------
     def admit(self, waiting: List[Sequence]) -> List[Sequence]:
@@ -76,6 +77,57 @@ class DecodeEngine:
                         continue                                # every slot is needed by the batch
                     mgr.deactivate_delta(victim)
                 mgr.activate_delta(d)
+            elif d > 0:
+                mgr._active_deltas.move_to_end(d)
+            in_use.add(d)
+            seq.blocks = self.cache.allocate(need)
+            admitted.append(seq)
+            waiting.remove(seq)
+        if admitted:
+            self.running.extend(admitted)
+            self._dirty = True
+        return admitted
+
+    def admit_overlapped(self, waiting: List[Sequence], ready=None) -> List[Sequence]:
+        """Admission that never makes the compute stream wait for a swap-in: a sequence whose
+        delta is not resident triggers a prefetch into a free (or evictable) GPU slot -- the
+        upload runs on the copy stream while the batch keeps decoding -- and joins in a later
+        round, once the upload's event has completed.  `ready(delta_id) -> bool` reports that
+        (default: the event's own query; a tensor-parallel caller passes the agreement of all
+        ranks so that every rank admits the same sequences)."""
+        mgr = self.manager
+        if ready is None:
+            def ready(d):
+                return mgr._slot_ready[mgr._loading[d]].query()
+        admitted = []
+        in_use = {s.delta_id for s in self.running if s.delta_id > 0}
+        wanted = set()
+        for seq in list(waiting):
+            if len(self.running) + len(admitted) >= self.max_seqs:
+                break
+            need = (seq.length + seq.max_new + self.block_size - 1) // self.block_size
+            if need > len(self.cache.free):
+                continue
+            d = seq.delta_id
+            if d > 0 and d not in mgr._active_deltas:
+                if mgr.get_delta(d) is None:
+                    continue
+                if d in mgr._loading:
+                    if not ready(d):
+                        continue
+                    mgr.activate_delta(d)              # upload finished: no stall
+                else:
+                    if d in wanted:
+                        continue
+                    if len(mgr._active_deltas) + len(mgr._loading) >= mgr.delta_slots:
+                        victim = next((x for x in mgr._active_deltas if x not in in_use), None)
+                        if victim is None:
+                            continue
+                        mgr.deactivate_delta(victim)
+                    mgr.prefetch_delta(d)
+                    self.swap_ins += 1
+                    wanted.add(d)
+                    continue
             elif d > 0:
                 mgr._active_deltas.move_to_end(d)
             in_use.add(d)
