@@ -187,6 +187,19 @@ def allreduce_selfcheck(car, rank, world, device):
                 got = car.all_reduce(x)
                 if bad is None and not torch.equal(got, want):
                     bad = f"mismatch variant={variant} dtype={dtype} numel={numel}"
+    if car.multicast:                        # in-switch reduction: one rounding of slack, ranks identical
+        car.set_variant(3)
+        for dtype, eps in ((torch.float16, 2.0 ** -10), (torch.bfloat16, 2.0 ** -7), (torch.float32, 2.0 ** -22)):
+            for numel in (8, 64 * 4096, 8 * 1237, 256 * 5120):
+                x = torch.randn(numel, generator=g, device=device).to(dtype)
+                want = expected(x).float()
+                got = car.all_reduce(x)
+                outs = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(outs, got)
+                same = all(torch.equal(o, outs[0]) for o in outs)
+                close = bool(((got.float() - want).abs() <= eps * want.abs() + 1e-6 * world).all())
+                if bad is None and not (same and close):
+                    bad = f"in-switch mismatch dtype={dtype} numel={numel} same={same} close={close}"
     car.set_variant(0)                       # from here on: chosen by size and rank count
     for it in range(100):                    # produced directly in the staging buffer
         st = car.staging_like((TOKENS, HIDDEN), torch.float16)
@@ -204,6 +217,36 @@ def allreduce_selfcheck(car, rank, world, device):
     if flag.item() == 0:
         return "ok"
     return bad if bad is not None else "mismatch on another rank"
+
+
+def pick_allreduce_kernel(car, world, device):
+    """Times the candidates for the benchmark's message ([64, 4096] fp16 produced in the staging
+    buffer) and returns the variant every rank agrees is fastest: the one-shot kernel (1) or,
+    where the regions have a multicast address, the in-switch kernel (3)."""
+    import torch
+    import torch.distributed as dist
+    candidates = [1] + ([3] if car.multicast else [])
+    if len(candidates) == 1:
+        return 0
+    out = torch.empty((TOKENS, HIDDEN), dtype=torch.float16, device=device)
+    took = []
+    for v in candidates:
+        car.set_variant(v)
+        for timed in (False, True):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0.record()
+            for _ in range(50):
+                st = car.staging_like((TOKENS, HIDDEN), torch.float16)
+                car.all_reduce(st, out=out)
+            e1.record()
+            torch.cuda.synchronize()
+        took.append(e0.elapsed_time(e1))
+    t = torch.tensor(took, device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    best = int(torch.argmin(t).item())
+    return candidates[best]
 
 
 def run_ours(args):
@@ -225,7 +268,10 @@ def run_ours(args):
             from deltazip_b200 import custom_all_reduce
             car = custom_all_reduce.init_custom_ar(rank, world)
             ar_check = allreduce_selfcheck(car, rank, world, device)
-            car.set_variant(args.ar_variant)
+            ar_choice = args.ar_variant
+            if args.ar_variant == 0 and ar_check == "ok":
+                ar_choice = pick_allreduce_kernel(car, world, device)
+            car.set_variant(ar_choice)
     tp = world
     L = _lib.lib()
 
@@ -442,9 +488,10 @@ def run_ours(args):
                 "parallelism": f"tp{world}",
                 "allreduce": ("fused: SBMM epilogue pushes tiles to every rank, local sum "
                               "(dz_allreduce_run_pushed)" if fused else
-                              "peer-memory (dz_allreduce_run, %s)" % (
-                                  {0: "one-shot kernel at this size", 1: "one-shot kernel (forced)",
-                                   2: "two-stage kernel (forced)"}[args.ar_variant])
+                              "peer-memory (dz_allreduce_run, %s%s)" % (
+                                  {0: "one-shot kernel at this size", 1: "one-shot kernel",
+                                   2: "two-stage kernel", 3: "in-switch multimem kernel"}[ar_choice],
+                                  ", timed against the alternatives at start-up" if args.ar_variant == 0 else ", forced")
                               if car is not None
                               else ("nccl" if world > 1 else "none")),
                 "l2": "inputs larger than L2: each step streams %.1f GB of distinct weights"
@@ -1184,8 +1231,9 @@ def main():
     ap.add_argument("--fused-ar", type=int, default=0, choices=[0, 1],
                     help="N>1: 1 = row-parallel SBMM pushes its tiles to all ranks, 0 = separate all-reduce "
                          "kernel fed from the staging buffer (default: measured faster)")
-    ap.add_argument("--ar-variant", type=int, default=0, choices=[0, 1, 2],
-                    help="peer-memory all-reduce kernel: 0 by size (default), 1 one-shot, 2 two-stage")
+    ap.add_argument("--ar-variant", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="peer-memory all-reduce kernel: 0 = the fastest of one-shot / in-switch, timed at "
+                         "start-up (default), 1 one-shot, 2 two-stage, 3 in-switch (multimem)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU sample (profiling captures)")
     ap.add_argument("--duration", type=float, default=None,
                     help="config 5: seconds of simulated arrivals (default 300)")

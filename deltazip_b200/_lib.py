@@ -109,6 +109,7 @@ _SIGNATURES = {
     "dz_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
     "dz_allreduce_region_bytes": (c_size_t, [c_size_t]),
     "dz_allreduce_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_size_t]),
+    "dz_allreduce_create_external": (c_int, [POINTER(c_void_p), c_int, c_int, c_size_t, POINTER(c_void_p), c_void_p]),
     "dz_allreduce_export": (c_int, [c_void_p, c_void_p]),
     "dz_allreduce_connect": (c_int, [c_void_p, c_void_p]),
     "dz_allreduce_staging": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_size_t)]),

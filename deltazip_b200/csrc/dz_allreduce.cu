@@ -32,9 +32,14 @@
 // SBMM's own tail; the reduction (dz_allreduce_run_pushed) only waits for flags that are usually
 // set already and sums slots in local memory, in rank order.
 //
+// Fourth form, for regions the caller allocated as symmetric memory with a multicast mapping
+// (dz_allreduce_create_external): after the same flag exchange, every rank reads its result with
+// multimem.ld_reduce -- the NVSwitch adds the ranks' copies in flight (fp32 accumulation) and one
+// load returns the sum, so a rank pulls the message once instead of (world - 1) times.
+//
 // A wait that does not complete within the time limit records DZ_ERR_TIMEOUT in the region's
 // status word and the kernel returns without reducing; nothing spins forever.
-// No multicast objects are used, only ordinary peer loads and stores.
+// The first three forms use ordinary peer loads and stores only.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -52,7 +57,10 @@ struct dz_allreduce_ctx {
   bool imported[8] = {false};
   unsigned epoch = 0;                      // calls so far
   bool connected = false;
-  int force_variant = 0;                   // 0: by size, 1: one-shot, 2: two-stage (tests / tuning)
+  int force_variant = 0;                   // 0: by size, 1: one-shot, 2: two-stage, 3: in-switch (tests / tuning)
+  bool owned = true;                       // region allocated (and IPC-exported) by this library
+  uint8_t* multicast = nullptr;            // multicast address of the regions (NVSwitch), or null
+  bool nvls_default = false;               // use the in-switch kernel when no variant is forced
 };
 
 namespace dz {
@@ -335,6 +343,63 @@ allreduce_twostage_kernel(const ArParams p) {
   }
 }
 
+// In-switch reduction: 16 bytes of the sum over all ranks from one multimem load.
+template <typename T> struct McLoad;
+template <> struct McLoad<__half> {
+  static __device__ __forceinline__ uint4 sum(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct McLoad<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 sum(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+template <> struct McLoad<float> {
+  static __device__ __forceinline__ uint4 sum(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+
+// Same slicing and flag exchange as the one-shot kernel; the sum comes from the switch.
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(kArThreads)
+allreduce_nvls_kernel(const ArParams p, const uint8_t* __restrict__ mc_region) {
+  __shared__ int s_abort;
+  const int b = blockIdx.x, nb = gridDim.x;
+  const long long nvec = p.count / Vec<T>::kN;
+  const long long per = (nvec + nb - 1) / nb;
+  const long long v0 = min(nvec, (long long)b * per), v1 = min(nvec, v0 + per);
+  uint8_t* const mine = p.peers[p.rank];
+  uint4* const my_stage =
+      reinterpret_cast<uint4*>(mine + kStagingOff + (size_t)p.parity * p.staging_bytes);
+  if (threadIdx.x == 0) s_abort = 0;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (p.copy_in) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.in);
+    for (long long i = v0 + threadIdx.x; i < v1; i += kArThreads) my_stage[i] = src[i];
+  }
+  __syncthreads();
+  publish_and_wait<WORLD>(p, kFlagsOff, b, p.copy_in != 0, &s_abort);
+  __syncthreads();
+  if (s_abort) return;
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  const uint4* mc_stage =
+      reinterpret_cast<const uint4*>(mc_region + kStagingOff + (size_t)p.parity * p.staging_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(p.out);
+  for (long long i = v0 + threadIdx.x; i < v1; i += kArThreads) dst[i] = McLoad<T>::sum(mc_stage + i);
+}
+
 // Reduction of tiles the producers pushed.  Block b handles output tile b (128 columns of every
 // row): it waits (bounded) until every source rank has raised the tile's flag for every token
 // block, then sums the `world` receive slots of the own region in rank order.
@@ -421,6 +486,28 @@ cudaError_t launch_pushed(const PushedParams& p, cudaStream_t st) {
 }
 
 template <typename T>
+cudaError_t launch_nvls(const ArParams& p, const uint8_t* mc, int blocks, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kArThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  switch (p.world) {
+    case 2: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 2>, p, mc);
+    case 3: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 3>, p, mc);
+    case 4: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 4>, p, mc);
+    case 5: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 5>, p, mc);
+    case 6: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 6>, p, mc);
+    case 7: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 7>, p, mc);
+    default: return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel<T, 8>, p, mc);
+  }
+}
+
+template <typename T>
 cudaError_t launch_allreduce(const ArParams& p, int blocks, bool two_stage, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
@@ -487,8 +574,30 @@ int dz_allreduce_create(dz_allreduce_ctx** out, int rank, int world, size_t max_
   return DZ_OK;
 }
 
+int dz_allreduce_create_external(dz_allreduce_ctx** out, int rank, int world, size_t max_bytes,
+                                 void* const* regions, void* multicast_region) {
+  if (!out || !regions || world < 1 || world > kMaxWorld || rank < 0 || rank >= world || max_bytes == 0)
+    return DZ_ERR_INVALID_ARG;
+  for (int r = 0; r < world; ++r)
+    if (!regions[r] || ((uintptr_t)regions[r] & 255)) return DZ_ERR_ALIGNMENT;
+  dz_allreduce_ctx* c = new (std::nothrow) dz_allreduce_ctx();
+  if (!c) return DZ_ERR_CUDA;
+  c->rank = rank;
+  c->world = world;
+  c->max_bytes = (max_bytes + 255) & ~(size_t)255;
+  c->region_bytes = dz_allreduce_region_bytes(max_bytes);
+  if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; return DZ_ERR_CUDA; }
+  c->owned = false;
+  for (int r = 0; r < world; ++r) c->peers[r] = reinterpret_cast<uint8_t*>(regions[r]);
+  c->region = c->peers[rank];
+  c->multicast = reinterpret_cast<uint8_t*>(multicast_region);
+  c->connected = true;
+  *out = c;
+  return DZ_OK;
+}
+
 int dz_allreduce_export(dz_allreduce_ctx* c, unsigned char* handle) {
-  if (!c || !handle) return DZ_ERR_INVALID_ARG;
+  if (!c || !handle || !c->owned) return DZ_ERR_INVALID_ARG;
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   cudaIpcMemHandle_t h;
   DZ_CUDA_OK(cudaIpcGetMemHandle(&h, c->region));
@@ -553,6 +662,19 @@ int dz_allreduce_run(dz_allreduce_ctx* c, const void* in, void* out, int64_t cou
   bool two_stage = c->world > 2 && bytes >= (size_t)4 * 1024 * 1024;
   if (c->force_variant == 1) two_stage = false;
   if (c->force_variant == 2 && c->world > 2) two_stage = true;
+  // in-switch reduction where the regions have a multicast mapping: forced, or by default from
+  // 64 KB up on more than two ranks (below that the plain one-shot kernel is as fast)
+  const bool nvls = c->multicast != nullptr && c->world > 1 &&
+                    (c->force_variant == 3 ||
+                     (c->force_variant == 0 && c->nvls_default && c->world > 2 && bytes >= 64 * 1024));
+  if (nvls) {
+    int nblocks = (int)((bytes + 8191) / 8192);
+    nblocks = nblocks < 1 ? 1 : (nblocks > kMaxBlocks ? kMaxBlocks : nblocks);
+    if (dtype == DZ_DTYPE_F16) DZ_CUDA_OK(launch_nvls<__half>(p, c->multicast, nblocks, st));
+    else if (dtype == DZ_DTYPE_BF16) DZ_CUDA_OK(launch_nvls<__nv_bfloat16>(p, c->multicast, nblocks, st));
+    else DZ_CUDA_OK(launch_nvls<float>(p, c->multicast, nblocks, st));
+    return DZ_OK;
+  }
   int blocks;
   if (two_stage) {
     // every block handles one sub-slice (~4 KB) of each of the `world` parts
@@ -611,8 +733,16 @@ int dz_allreduce_run_pushed(dz_allreduce_ctx* c, void* out, int M, int N, int dt
 }
 
 int dz_allreduce_set_variant(dz_allreduce_ctx* c, int variant) {
-  if (!c || variant < 0 || variant > 2) return DZ_ERR_INVALID_ARG;
+  if (!c || variant < 0 || variant > 4) return DZ_ERR_INVALID_ARG;
+  if (variant == 3 && !c->multicast) return DZ_ERR_UNSUPPORTED;
+  if (variant == 4) {                      // "by size, in-switch kernel allowed"
+    if (!c->multicast) return DZ_ERR_UNSUPPORTED;
+    c->force_variant = 0;
+    c->nvls_default = true;
+    return DZ_OK;
+  }
   c->force_variant = variant;
+  if (variant == 0) c->nvls_default = false;
   return DZ_OK;
 }
 
@@ -626,7 +756,7 @@ int dz_allreduce_destroy(dz_allreduce_ctx* c) {
   if (!c) return DZ_OK;
   for (int r = 0; r < c->world; ++r)
     if (c->imported[r]) cudaIpcCloseMemHandle(c->peers[r]);
-  if (c->region) cudaFree(c->region);
+  if (c->region && c->owned) cudaFree(c->region);
   delete c;
   return DZ_OK;
 }

@@ -14,6 +14,7 @@ removes the copy-in the reference pays outside CUDA graphs.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -31,13 +32,20 @@ class CustomAllreduce:
     collectively and issue the same sequence of `all_reduce` calls."""
 
     def __init__(self, rank: int, world_size: int, max_size: int = 8192 * 1024,
-                 group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None):
+                 group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None,
+                 symmetric: Optional[bool] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("CustomAllreduce needs CUDA devices")
         self.rank, self.world_size, self.max_size = rank, world_size, max_size
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self._ctx = ctypes.c_void_p()
+        self.multicast = False
+        self._symm = None
+        if symmetric is None:
+            symmetric = os.environ.get("DZ_AR_SYMMETRIC", "1") != "0"
         with torch.cuda.device(self.device):
+            if world_size > 1 and symmetric and self._create_symmetric(group):
+                return
             check(lib().dz_allreduce_create(ctypes.byref(self._ctx), rank, world_size, max_size),
                   "dz_allreduce_create")
             handle = (ctypes.c_ubyte * 64)()
@@ -50,6 +58,39 @@ class CustomAllreduce:
                 buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
                 check(lib().dz_allreduce_connect(self._ctx, buf), "dz_allreduce_connect")
                 dist.barrier(group=group)   # every region is mapped everywhere before first use
+
+    def _create_symmetric(self, group) -> bool:
+        """Regions in torch's symmetric memory (PyTorch as the allocator: it maps every rank's
+        buffer into every process and, on NVSwitch machines, binds them to one multicast
+        address).  All ranks succeed or fall back together.  With a multicast address the
+        in-switch kernel becomes available (`set_variant(3)` / `set_variant(4)`)."""
+        ok, ptrs, mc, region, hdl = 1, None, 0, None, None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            nbytes = lib().dz_allreduce_region_bytes(self.max_size)
+            region = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            region.zero_()
+            torch.cuda.synchronize(self.device)
+            hdl = symm_mem.rendezvous(region, group if group is not None else dist.group.WORLD)
+            ptrs, mc = list(hdl.buffer_ptrs), int(hdl.multicast_ptr or 0)
+            if len(ptrs) != self.world_size or any(p == 0 or p % 256 for p in ptrs):
+                ok = 0
+        except Exception:                                      # noqa: BLE001 -- any failure: IPC path
+            ok = 0
+        flag = torch.tensor([ok, 1 if mc else 0], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag[0].item()) == 0:
+            return False
+        if int(flag[1].item()) == 0:
+            mc = 0
+        arr = (ctypes.c_void_p * self.world_size)(*ptrs)
+        check(lib().dz_allreduce_create_external(ctypes.byref(self._ctx), self.rank, self.world_size,
+                                                 self.max_size, arr, ctypes.c_void_p(mc or None)),
+              "dz_allreduce_create_external")
+        self._symm = (region, hdl)                             # keep the mapping alive
+        self.multicast = bool(mc)
+        dist.barrier(group=group)
+        return True
 
     def should_custom_ar(self, inp: torch.Tensor) -> bool:
         nbytes = inp.numel() * inp.element_size()
@@ -107,7 +148,9 @@ class CustomAllreduce:
 
     def set_variant(self, variant: int) -> None:
         """0: kernel chosen by message size and rank count; 1: always the one-shot kernel;
-        2: the two-stage kernel whenever there are more than two ranks (all ranks alike)."""
+        2: the two-stage kernel whenever there are more than two ranks; 3: always the in-switch
+        (multimem) kernel; 4: like 0 with the in-switch kernel from 64 KB on more than two ranks
+        (3 and 4 need `self.multicast`).  All ranks alike."""
         check(lib().dz_allreduce_set_variant(self._ctx, variant), "dz_allreduce_set_variant")
 
     def status(self) -> int:

@@ -341,6 +341,15 @@ int dz_slot_reset(void* dst_device, size_t bytes, void* stream);
 typedef struct dz_allreduce_ctx dz_allreduce_ctx;
 size_t dz_allreduce_region_bytes(size_t max_bytes);
 int dz_allreduce_create(dz_allreduce_ctx** ctx, int rank, int world, size_t max_bytes);
+/* Same context over regions the CALLER allocated, one per rank, each dz_allreduce_region_bytes()
+ * large, 256-byte aligned, peer-accessible from this rank (regions[r] = this process's address of
+ * rank r's region), with their first 16 KB zero-filled on every rank before any run -- e.g.
+ * symmetric memory.  `multicast_region` (may be NULL) is the address under which one access
+ * reaches all ranks' regions through the NVSwitch; with it, variant 3 / 4 of
+ * dz_allreduce_set_variant reads sums with multimem.ld_reduce (in-switch reduction).  No export /
+ * connect step; destroy leaves the regions alone. */
+int dz_allreduce_create_external(dz_allreduce_ctx** ctx, int rank, int world, size_t max_bytes,
+                                 void* const* regions, void* multicast_region);
 int dz_allreduce_export(dz_allreduce_ctx* ctx, unsigned char* handle64);
 int dz_allreduce_connect(dz_allreduce_ctx* ctx, const unsigned char* handles);
 int dz_allreduce_staging(dz_allreduce_ctx* ctx, void** ptr, size_t* bytes);
@@ -360,9 +369,11 @@ int dz_allreduce_status(dz_allreduce_ctx* ctx, int* status);
 int dz_allreduce_push_target(dz_allreduce_ctx* ctx, int M, int N, int dtype, dz_push_target* target);
 int dz_allreduce_run_pushed(dz_allreduce_ctx* ctx, void* out, int M, int N, int dtype, void* stream);
 /* Kernel choice of later runs: 0 = by message size and rank count (one kernel that sums whole
- * slices for small messages, a reduce-scatter + all-gather kernel above the sizes at which
- * serving/csrc/custom_all_reduce.cuh:443-456 switches), 1 = always the former, 2 = the latter
- * whenever there are more than two ranks.  Every rank must make the same choice. */
+ * slices for decode-size messages, a reduce-scatter + all-gather kernel for large ones; the
+ * reference switches the same way, serving/csrc/custom_all_reduce.cuh:443-456), 1 = always the
+ * former, 2 = the latter whenever there are more than two ranks, 3 = always the in-switch kernel
+ * (needs a multicast region), 4 = like 0 but with the in-switch kernel for messages of 64 KB and
+ * more on more than two ranks.  Every rank must make the same choice. */
 int dz_allreduce_set_variant(dz_allreduce_ctx* ctx, int variant);
 int dz_allreduce_destroy(dz_allreduce_ctx* ctx);
 

@@ -64,6 +64,27 @@ def main():
             outs = [torch.empty_like(got) for _ in range(world)]
             dist.all_gather(outs, got)
             assert all(torch.equal(o, outs[0]) for o in outs), "ranks disagree"
+    # --- in-switch reduction (regions in symmetric memory with a multicast address): the switch
+    #     adds in its own order, so values are compared to within one rounding of the result
+    #     type, and all ranks must hold identical bits ---
+    if h.multicast:
+        h.set_variant(3)
+        for dtype in (torch.float16, torch.bfloat16, torch.float32):
+            for numel in (8, 4096, 64 * 4096, 8 * 1237, 2 * 1024 * 1024):
+                x = torch.randn(numel, device=dev, dtype=torch.float32, generator=g).to(dtype)
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                want = expected_sum(parts, dtype).float()
+                got = h.all_reduce(x)
+                torch.cuda.synchronize()
+                eps = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7, torch.float32: 2.0 ** -22}[dtype]
+                assert ((got.float() - want).abs() <= eps * want.abs() + 1e-6 * world).all(), (dtype, numel)
+                outs = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(outs, got)
+                assert all(torch.equal(o, outs[0]) for o in outs), "ranks disagree (in-switch)"
+        h.set_variant(0)
+    print(f"rank {rank}: symmetric={h._symm is not None} multicast={h.multicast}", flush=True)
+
     # --- messages that do not qualify fall back (None) ---
     assert custom_all_reduce.custom_all_reduce(torch.zeros(3, device=dev, dtype=torch.float16)) is None
     big = torch.zeros(h.max_size // 2 + 8, device=dev, dtype=torch.float16)
@@ -74,7 +95,8 @@ def main():
     # --- staging path + many back-to-back calls with changing data (buffer alternation) ---
     shape = (64, 4096)
     for it in range(200):
-        h.set_variant(1 + (it // 25) % 2)       # alternate the two kernels every 25 calls
+        # alternate the kernels every 25 calls (in-switch too where it exists)
+        h.set_variant((1, 2, 3)[(it // 25) % 3] if h.multicast else 1 + (it // 25) % 2)
         st = h.staging_like(shape, torch.float16)
         st.copy_(torch.full(shape, float(rank + 1 + (it % 7)), device=dev, dtype=torch.float16))
         out = h.all_reduce(st)
@@ -138,6 +160,7 @@ def main():
     # --- bounded wait: rank 0 issues a call nobody joins ---
     dist.barrier()
     torch.cuda.synchronize()
+    h.set_variant(1)                        # plain peer loads only while a rank waits alone
     if rank == 0:
         lonely = torch.ones(4096, device=dev, dtype=torch.float16)
         h.all_reduce(lonely)
