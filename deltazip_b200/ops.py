@@ -7,7 +7,13 @@
 
 All tensors are CUDA tensors; work is enqueued on torch's current stream.
 PyTorch is used for memory and streams only -- every computation below runs in
-libdeltazip_b200.so.
+libdeltazip_b200.so, with one exception: for prefill-sized batches (more than
+FUSED_MAX_TOKENS rows) the plain dense product x W^T, the reference's F.linear
+(serving/vllm/model_executor/layers/linear.py:85-96), goes to the library GEMM
+(torch.matmul) once, and the library's kernel then adds the delta products into
+that result token block by token block.  The fused kernel streams W once per
+block of 128 tokens, which is the right trade for decode batches and the wrong
+one for thousands of prompt tokens.
 """
 from __future__ import annotations
 
@@ -18,6 +24,10 @@ import torch
 
 from . import _lib
 from ._lib import SbmmArgs, check, lib
+
+
+# Largest batch (rows of x) that takes the fused kernel for base and delta products together.
+FUSED_MAX_TOKENS = 512
 
 
 def _stream() -> int:
@@ -213,6 +223,22 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
         raise ValueError(f"segment table was built for {segments.m} tokens, x has {m}")
     if bits is None:
         bits = _bits_from_shapes(qweight_stacked, k)
+    if base_weight is not None and m > FUSED_MAX_TOKENS and push is None and _entry == "dz_sbmm":
+        # prefill-sized batch: the dense product once through the library GEMM, then the
+        # delta products added to it in place (not the early-start form: y is the
+        # predecessor's output here)
+        base = torch.matmul(x2, base_weight.t())
+        if out is None:
+            out = base
+        else:
+            o2 = out.reshape(-1, out.shape[-1]) if out.dim() != 2 else out
+            if accumulate:
+                o2.add_(base)
+            else:
+                o2.copy_(base)
+        sbmm(x2, qweight_stacked, scales_stacked, meta_stacked, segments, None, out=out,
+             bits=bits, accumulate=True)
+        return out.reshape(*x.shape[:-1], n) if out.is_contiguous() else out
     if push is not None:
         if accumulate or out is not None or m == 0:
             raise ValueError("a pushed output takes neither `out` nor `accumulate`, and needs rows")
@@ -266,13 +292,19 @@ def stream_fence() -> None:
 
 def base_gemm(x: torch.Tensor, base_weight: torch.Tensor,
               out: Optional[torch.Tensor] = None, stable: bool = False) -> torch.Tensor:
-    """y = x W^T on the same kernel (every token base-only)."""
+    """y = x W^T on the same kernel (every token base-only); the library GEMM for more than
+    FUSED_MAX_TOKENS rows."""
     _need_cuda(x, base_weight)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
     m, k = x2.shape
     n = base_weight.shape[0]
+    if m > FUSED_MAX_TOKENS:
+        if out is None:
+            return torch.matmul(x2, base_weight.t()).reshape(*x.shape[:-1], n)
+        torch.matmul(x2, base_weight.t(), out=out.reshape(m, n))
+        return out.reshape(*x.shape[:-1], n)
     if out is None:
         out = torch.empty((m, n), dtype=x.dtype, device=x.device)
     if m == 0:

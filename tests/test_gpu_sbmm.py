@@ -253,3 +253,45 @@ def test_apply_delta_sees_new_and_rewritten_index_tensors():
     # repeated calls on an unchanged tensor reuse the table and agree bit for bit
     yd = ops.apply_delta(xd, layer.qweight, layer.scales, layer.meta, ib, layer.w).cpu().numpy()
     np.testing.assert_array_equal(yc.view(np.uint16), yd.view(np.uint16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 4])
+def test_prefill_sized_batch_takes_the_split_path_and_agrees_with_the_fused_one(bits):
+    """More than ops.FUSED_MAX_TOKENS rows: dense product through the library GEMM, delta
+    products added in place by the kernel.  Checked against dequantise-then-matmul in fp32
+    (rel-L2 <= 1e-2, the tolerance of the layer outputs) and against the fused kernel on the
+    same inputs (the two differ by one fp16 rounding of the base product)."""
+    from deltazip_b200 import ops, synth
+    dev = torch.device("cuda")
+    n, k, slots, m = 1024, 1536, 5, 1500
+    g = torch.Generator(device=dev).manual_seed(7)
+    w = (torch.randn((n, k), generator=g, device=dev) * 0.02).half()
+    x = torch.randn((m, k), generator=g, device=dev).half()
+    qw, meta, sc = synth.random_delta_slots(slots, n, k, bits, seed=3, device=dev, std=1e-2)
+    idx = torch.sort(torch.randint(-1, slots, (m,), generator=g, device=dev))[0]
+    seg = ops.Segments(m, slots, dev).build(idx)
+    assert m > ops.FUSED_MAX_TOKENS
+    got = ops.sbmm(x, qw, sc, meta, seg, w)
+    want = x.float() @ w.float().t()
+    for s in range(slots):
+        rows = (idx == s).nonzero().flatten()
+        want[rows] += x[rows].float() @ ops.unpack(qw[s], meta[s], sc[s], n, k, bits).float().t()
+    rel = ((got.float() - want).norm() / want.norm()).item()
+    assert rel <= 1e-2, rel
+    keep = ops.FUSED_MAX_TOKENS
+    try:
+        ops.FUSED_MAX_TOKENS = 1 << 30
+        fused = ops.sbmm(x, qw, sc, meta, seg, w)
+    finally:
+        ops.FUSED_MAX_TOKENS = keep
+    rel2 = ((got.float() - fused.float()).norm() / fused.float().norm()).item()
+    assert rel2 <= 2e-3, rel2
+    # into a column slice of a wider tensor, and the base product alone
+    wide = torch.zeros((m, n + 256), device=dev, dtype=torch.float16)
+    ops.sbmm(x, qw, sc, meta, seg, w, out=wide[:, 128:128 + n])
+    assert torch.equal(wide[:, 128:128 + n], got) and not wide[:, :128].any() and not wide[:, 128 + n:].any()
+    base = ops.base_gemm(x, w)
+    assert ((base.float() - x.float() @ w.float().t()).norm() / want.norm()).item() <= 2e-3
+    torch.cuda.synchronize()
+    assert ops.read_status(dev) == 0
