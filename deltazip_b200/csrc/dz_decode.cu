@@ -228,6 +228,98 @@ paged_decode_attention_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
   const int t0 = split * per, t1 = min(len, t0 + per);
   const int q_heads = kv_heads * G;
 
+  const int* table = block_tables + (size_t)seq * max_blocks;
+  if constexpr (G <= 2) {
+    // Few query heads per key/value head: the kernel is a pure stream of K and V rows, so what
+    // counts is bytes in flight.  A half-warp owns a row (16 lanes x 16 bytes), a warp two rows
+    // per load instruction, and two such pairs are requested per iteration: 64 bytes in flight
+    // per lane.  Each half-warp keeps its own running (max, sum, accumulator); the halves are
+    // merged by shuffles at the end, the warps through shared memory as in the general form.
+    const int half = lane >> 4, hl = lane & 15;
+    float q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const uint4 v = *reinterpret_cast<const uint4*>(qkv + (size_t)seq * q_row_stride +
+                                                      (size_t)(kh * G + g) * kHeadDim + hl * 8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Cvt<T>::up(w[j]);
+        q[g][2 * j] = f.x * scale;
+        q[g][2 * j + 1] = f.y * scale;
+      }
+    }
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+    }
+    for (int base = t0 + 2 * warp; base < t1; base += 4 * kWarps) {
+      const int ta = base + half, tb = ta + 2 * kWarps;
+      const bool va_ok = ta < t1, vb_ok = tb < t1;
+      const int tac = min(ta, t1 - 1), tbc = min(tb, t1 - 1);     // rows read for absent tokens
+      const size_t ra = ((size_t)table[tac / block_size] * block_size + tac % block_size) * kv_heads + kh;
+      const size_t rb = ((size_t)table[tbc / block_size] * block_size + tbc % block_size) * kv_heads + kh;
+      const uint4 ka = *reinterpret_cast<const uint4*>(k_cache + ra * kHeadDim + hl * 8);
+      const uint4 kb = *reinterpret_cast<const uint4*>(k_cache + rb * kHeadDim + hl * 8);
+      const uint4 va = *reinterpret_cast<const uint4*>(v_cache + ra * kHeadDim + hl * 8);
+      const uint4 vb = *reinterpret_cast<const uint4*>(v_cache + rb * kHeadDim + hl * 8);
+      float fka[8], fkb[8], fva[8], fvb[8];
+      {
+        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
+        const uint32_t xa[4] = {va.x, va.y, va.z, va.w}, xb[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = Cvt<T>::up(wa[j]); fka[2 * j] = f.x; fka[2 * j + 1] = f.y;
+          f = Cvt<T>::up(wb[j]); fkb[2 * j] = f.x; fkb[2 * j + 1] = f.y;
+          f = Cvt<T>::up(xa[j]); fva[2 * j] = f.x; fva[2 * j + 1] = f.y;
+          f = Cvt<T>::up(xb[j]); fvb[2 * j] = f.x; fvb[2 * j + 1] = f.y;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { sa += q[g][j] * fka[j]; sb += q[g][j] * fkb[j]; }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {            // within the half-warp
+          sa += __shfl_xor_sync(0xffffffffu, sa, o);
+          sb += __shfl_xor_sync(0xffffffffu, sb, o);
+        }
+        if (va_ok) {                                  // vb_ok implies va_ok
+          if (!vb_ok) sb = -INFINITY;
+          const float mn = fmaxf(m[g], fmaxf(sa, sb));
+          const float c = __expf(m[g] - mn), pa = __expf(sa - mn), pb = __expf(sb - mn);
+          l[g] = l[g] * c + pa + pb;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * c + pa * fva[j] + pb * fvb[j];
+          m[g] = mn;
+        }
+      }
+    }
+    // merge the two half-warps, then hand the warp's state to shared memory
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], 16);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[g], 16);
+      const float mm = fmaxf(m[g], mo);
+      const float c0 = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - mm);
+      const float c1 = (mo == -INFINITY) ? 0.f : __expf(mo - mm);
+      const float ll = l[g] * c0 + lo * c1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], 16);
+        acc[g][j] = acc[g][j] * c0 + ao * c1;
+      }
+      if (lane == 0) { s_m[warp][g] = mm; s_l[warp][g] = ll; }
+      if (half == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s_acc[warp][g][hl * 8 + j] = acc[g][j];
+      }
+    }
+  } else {
   float q[G][4];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -242,7 +334,6 @@ paged_decode_attention_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
     m[g] = -INFINITY; l[g] = 0.f;
     acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
   }
-  const int* table = block_tables + (size_t)seq * max_blocks;
   // two tokens per iteration keep four 8-byte loads per lane in flight
   for (int t = t0 + warp; t < t1; t += 2 * kWarps) {
     const int tb = t + kWarps;
@@ -279,6 +370,7 @@ paged_decode_attention_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
     if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
 #pragma unroll
     for (int j = 0; j < 4; ++j) s_acc[warp][g][lane * 4 + j] = acc[g][j];
+  }
   }
   __syncthreads();
   // thread (g, d) pairs: G * 128 values, 256 threads
@@ -442,7 +534,7 @@ int dz_paged_attention_decode(const void* qkv, int q_row_stride, void* out, cons
       max_blocks <= 0 || splits < 1 || splits > 64)
     return DZ_ERR_INVALID_ARG;
   if (head_dim != kHeadDim) return DZ_ERR_SHAPE;
-  if ((q_row_stride & 3) || !aligned16(qkv) || !aligned16(out) || !aligned16(k_cache) ||
+  if ((q_row_stride & 7) || !aligned16(qkv) || !aligned16(out) || !aligned16(k_cache) ||
       !aligned16(v_cache))
     return DZ_ERR_ALIGNMENT;
   if (dtype != DZ_DTYPE_F16 && dtype != DZ_DTYPE_BF16) return DZ_ERR_INVALID_ARG;

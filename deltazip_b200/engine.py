@@ -49,7 +49,7 @@ class DecodeEngine:
         self.tokens = None
         self.positions = None
         self.block_tables = None
-        self.attn_splits = 1
+        self.attn_splits = 0            # 0: chosen per step from the batch (see decode_step)
         self.swap_ins = 0
 
     # -- batch composition -----------------------------------------------------------
@@ -186,9 +186,12 @@ class DecodeEngine:
         blk = torch.gather(self.block_tables, 1, (pos // bs).unsqueeze(1)).squeeze(1).to(torch.int64)
         slot = blk * bs + pos % bs
         lens = (pos + 1).to(torch.int32)
+        # one CTA per (sequence, kv head, split): split the keys when the batch alone would leave
+        # most SMs without a CTA
+        splits = self.attn_splits or max(1, min(8, 296 // max(1, len(self.running) * self.model.kv_heads)))
         h = self.model(self.tokens, pos, self.cache,
                        AttnMeta(slot_mapping=slot, block_tables=self.block_tables, seq_lens=lens,
-                                splits=self.attn_splits))
+                                splits=splits))
         self.tokens = self.model.greedy_tokens(h)
         self.positions = pos + 1
         for s in self.running:
