@@ -154,7 +154,9 @@ silu_and_mul_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int in
 // Rotary position embedding (neox style: dims d and d + 64 form a pair) applied in place to the
 // q and k parts of a fused qkv row, followed by the write of the rotated k and of v into the
 // paged cache at `slot_mapping[token]` (block * block_size + offset; < 0 = not cached).
-// One CTA per token, one warp per head in turn; a lane owns dims [2l, 2l+2) and [64+2l, 64+2l+2).
+// Grid (tokens, heads / 4): one warp per (token, head), so every warp makes one round trip to
+// memory instead of walking the heads of its token one after another; a lane owns dims
+// [2l, 2l+2) and [64+2l, 64+2l+2).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -175,7 +177,8 @@ rotary_cache_kernel(T* __restrict__ qkv, const int64_t* __restrict__ positions,
     const float inv_freq = exp2f(-log2_theta * (float)(2 * (2 * lane + j)) / (float)kHeadDim);
     sincosf(pos * inv_freq, &sn[j], &cs[j]);
   }
-  for (int h = warp; h < q_heads + 2 * kv_heads; h += 4) {
+  const int h = blockIdx.y * 4 + warp;
+  if (h < q_heads + 2 * kv_heads) {
     uint32_t* p = reinterpret_cast<uint32_t*>(row + (size_t)h * kHeadDim);
     uint32_t lo = p[lane], hi = p[32 + lane];
     if (h < q_heads + kv_heads) {
@@ -507,11 +510,12 @@ int dz_rotary_and_cache(void* qkv, const int64_t* positions, const int64_t* slot
   if (M == 0) return DZ_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const float l2t = log2f(rope_theta);
+  const dim3 grid(M, (q_heads + 2 * kv_heads + 3) / 4);
   if (dtype == DZ_DTYPE_F16)
-    DZ_CUDA_OK(launch_pdl(rotary_cache_kernel<__half>, dim3(M), dim3(128), st, (__half*)qkv, positions,
+    DZ_CUDA_OK(launch_pdl(rotary_cache_kernel<__half>, grid, dim3(128), st, (__half*)qkv, positions,
                           slot_mapping, (__half*)k_cache, (__half*)v_cache, q_heads, kv_heads, l2t));
   else
-    DZ_CUDA_OK(launch_pdl(rotary_cache_kernel<__nv_bfloat16>, dim3(M), dim3(128), st,
+    DZ_CUDA_OK(launch_pdl(rotary_cache_kernel<__nv_bfloat16>, grid, dim3(128), st,
                           (__nv_bfloat16*)qkv, positions, slot_mapping, (__nv_bfloat16*)k_cache,
                           (__nv_bfloat16*)v_cache, q_heads, kv_heads, l2t));
   return DZ_OK;
