@@ -846,9 +846,10 @@ def run_decode(args):
         pms = p0.elapsed_time(p1)
         prefill_info = {"tokens": timed_tokens, "ms": pms, "chunk_tokens": per * prompt,
                         "tok_s": (timed_tokens / (pms * 1e-3)) if pms > 0 else None,
-                        "note": "dense product of a chunk through the library GEMM, delta products "
-                                "added by the SBMM kernel per block of 128 tokens; causal attention "
-                                "through torch's SDPA"}
+                        "note": "dense product of a chunk through the library GEMM; delta products "
+                                "of runs of 256 and more rows of one delta through dz_unpack + the "
+                                "library GEMM, of shorter runs by the SBMM kernel per block of 128 "
+                                "tokens; causal attention through torch's SDPA"}
     else:
         # prefill is replaced by a synthetic cache of the prompt length: random keys and values
         for li in range(layers):

@@ -44,7 +44,8 @@ def _convert_mapping(mapping: DeltaMapping, delta_index_to_id: List[Optional[int
     The slot of every token comes from one table lookup over the whole batch (the reference
     searches the slot list once per token); the lookup and the "is this delta active" check run
     on the host's copy of the ids, and the five tensors reach the device in one copy, so nothing
-    here waits for the GPU.  Also returns whether the token slots are non-decreasing."""
+    here waits for the GPU.  Also returns (whether the token slots are non-decreasing, and for a
+    sorted batch of more than ops.FUSED_MAX_TOKENS rows its runs [(slot, first row, end row)])."""
     ids = torch.tensor([0 if x is None else x for x in mapping.index_mapping], dtype=torch.long)
     prompt_ids = torch.tensor([0 if x is None else x for x in mapping.prompt_mapping], dtype=torch.long)
     active = [d for d in delta_index_to_id if d is not None]
@@ -77,8 +78,13 @@ def _convert_mapping(mapping: DeltaMapping, delta_index_to_id: List[Optional[int
     sampler_indices_padded = on_dev[3, :s]
     indices_len = (n, s, s, n)
     is_sorted = bool(n < 2 or (slots[1:] >= slots[:-1]).all())
+    runs = None
+    if is_sorted and n > ops.FUSED_MAX_TOKENS:
+        # prefill-sized batch: the runs of equal slots (host side), for the dequantise-once path
+        cuts = (torch.nonzero(slots[1:] != slots[:-1]).flatten() + 1).tolist()
+        runs = [(int(slots[a]), a, b) for a, b in zip([0] + cuts, cuts + [n])]
     return (base_indices, sampler_indices, sampler_indices_padded, embeddings_indices,
-            indices_len), is_sorted
+            indices_len), (is_sorted, runs)
 
 
 def convert_mapping(mapping: DeltaMapping, delta_index_to_id: List[Optional[int]], max_deltas: int,
@@ -620,7 +626,7 @@ class DeltaModelManager:
 
     # -- mapping -------------------------------------------------------------------
     def _set_delta_mapping(self, mapping: DeltaMapping) -> None:
-        (base, sampler, padded, emb, indices_len), is_sorted = _convert_mapping(
+        (base, sampler, padded, emb, indices_len), (is_sorted, runs) = _convert_mapping(
             mapping, self.delta_index_to_id, self.delta_slots + 1, self.vocab_size,
             self.delta_config.delta_extra_vocab_size, device=self.device)
         self.base_indices[: base.shape[0]].copy_(base)
@@ -630,6 +636,7 @@ class DeltaModelManager:
         self.indices_len[:] = indices_len
         # the host already knows the slot order: no device round trip for the sorted promise
         self.segments.build(self.base_indices[: base.shape[0]], sorted_hint=is_sorted)
+        self.segments.host_runs = runs
 
     def set_delta_mapping(self, mapping: DeltaMapping) -> None:
         if self._last_mapping != mapping:

@@ -28,6 +28,11 @@ from ._lib import SbmmArgs, check, lib
 
 # Largest batch (rows of x) that takes the fused kernel for base and delta products together.
 FUSED_MAX_TOKENS = 512
+# In a prefill-sized, sorted batch whose host-side run list is known (Segments.host_runs), a slot
+# with at least this many consecutive rows is dequantised once (dz_unpack) and multiplied by the
+# library GEMM, as the reference's PyTorch path does (deltazip/nn_modules/qlinear.py:266-330);
+# the SBMM kernel would expand the slot's codes once per 32-row window instead.
+DENSE_RUN_TOKENS = 256
 
 
 def _stream() -> int:
@@ -116,6 +121,9 @@ class Segments:
         self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         self.m = 0
         self.sorted = False
+        # [(slot, first row, end row)] of a sorted batch when the caller knows it on the host
+        # (the slot manager does); None otherwise.  Only prefill-sized batches use it.
+        self.host_runs = None
 
     def build(self, indices: torch.Tensor, sorted_hint: Optional[bool] = None) -> "Segments":
         """Builds the table on the current stream; never synchronises with the host.
@@ -139,6 +147,7 @@ class Segments:
                                       self.buf.data_ptr(), _stream()), "dz_build_segments")
         self.m = m
         self.sorted = bool(sorted_hint)
+        self.host_runs = None
         return self
 
     def is_sorted_on_device(self) -> bool:
@@ -236,8 +245,19 @@ def sbmm(x: torch.Tensor, qweight_stacked: torch.Tensor, scales_stacked: torch.T
                 o2.add_(base)
             else:
                 o2.copy_(base)
-        sbmm(x2, qweight_stacked, scales_stacked, meta_stacked, segments, None, out=out,
-             bits=bits, accumulate=True)
+        runs = segments.host_runs
+        if runs is not None and segments.sorted and \
+                all(e - s >= DENSE_RUN_TOKENS for slot, s, e in runs if slot >= 0):
+            o2 = out.reshape(-1, out.shape[-1]) if out.dim() != 2 else out
+            for slot, s, e in runs:
+                if slot < 0:
+                    continue
+                dense = unpack(qweight_stacked[slot], meta_stacked[slot], scales_stacked[slot],
+                               n, k, bits)
+                o2[s:e].addmm_(x2[s:e], dense.to(x2.dtype).t())
+        else:
+            sbmm(x2, qweight_stacked, scales_stacked, meta_stacked, segments, None, out=out,
+                 bits=bits, accumulate=True)
         return out.reshape(*x.shape[:-1], n) if out.is_contiguous() else out
     if push is not None:
         if accumulate or out is not None or m == 0:

@@ -295,3 +295,43 @@ def test_prefill_sized_batch_takes_the_split_path_and_agrees_with_the_fused_one(
     assert ((base.float() - x.float() @ w.float().t()).norm() / want.norm()).item() <= 2e-3
     torch.cuda.synchronize()
     assert ops.read_status(dev) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 4])
+def test_prefill_runs_known_on_the_host_take_the_dequantise_once_path(bits):
+    """A sorted prefill-sized batch whose runs the caller knows (Segments.host_runs, as the slot
+    manager provides) multiplies each long run by the slot's dequantised delta through the
+    library GEMM; the result must agree with the kernel path and with the fp32 reference."""
+    from deltazip_b200 import ops, synth
+    dev = torch.device("cuda")
+    n, k, slots = 1024, 1024, 3
+    lens = [300, 600, 256, 400]                      # base rows, slot 0, slot 1, slot 2
+    idx = torch.cat([torch.full((c,), s - 1, dtype=torch.int64) for s, c in enumerate(lens)]).to(dev)
+    m = idx.numel()
+    g = torch.Generator(device=dev).manual_seed(11)
+    w = (torch.randn((n, k), generator=g, device=dev) * 0.02).half()
+    x = torch.randn((m, k), generator=g, device=dev).half()
+    qw, meta, sc = synth.random_delta_slots(slots, n, k, bits, seed=5, device=dev, std=1e-2)
+    seg = ops.Segments(m, slots, dev).build(idx, sorted_hint=True)
+    kernel_path = ops.sbmm(x, qw, sc, meta, seg, w)
+    edges = [0]
+    for c in lens:
+        edges.append(edges[-1] + c)
+    seg.host_runs = [(s - 1, edges[s], edges[s + 1]) for s in range(len(lens))]
+    dense_path = ops.sbmm(x, qw, sc, meta, seg, w)
+    want = x.float() @ w.float().t()
+    for s in range(slots):
+        rows = (idx == s).nonzero().flatten()
+        want[rows] += x[rows].float() @ ops.unpack(qw[s], meta[s], sc[s], n, k, bits).float().t()
+    assert ((dense_path.float() - want).norm() / want.norm()).item() <= 2e-3
+    assert ((dense_path.float() - kernel_path.float()).norm() / want.norm()).item() <= 2e-3
+    # a short run sends the whole call back to the kernel
+    seg.host_runs = [(-1, 0, 300), (0, 300, 900), (1, 900, 1000), (1, 1000, 1156), (2, 1156, m)]
+    again = ops.sbmm(x, qw, sc, meta, seg, w)
+    assert torch.equal(again, kernel_path)
+    # the slot manager's mapping yields the runs for such a batch
+    from deltazip_b200.models import DeltaMapping, _convert_mapping
+    ids = [0] * 300 + [7] * 600 + [9] * 700
+    _, (is_sorted, runs) = _convert_mapping(DeltaMapping(ids, [0, 7, 9]), [7, 9, None], 4, 32000, 0, device=dev)
+    assert is_sorted and runs == [(-1, 0, 300), (0, 300, 900), (1, 900, 1600)]
