@@ -11,7 +11,8 @@
 //   delta : the packed codes and 2:4 metadata of (slot, tile, k-unit) arrive by
 //           bulk copy; a warpgroup expands the codes to the *compressed* fp16 A
 //           operand directly into tensor memory (one row per thread, one logic
-//           op + one subtract + one multiply per fp16 pair, tcgen05.st), stores
+//           op + one subtract per fp16 pair, tcgen05.st; the per-channel scale
+//           is applied to the accumulated sums in the epilogue), stores
 //           the metadata next to it, and copies the slot's token window out of
 //           the resident x tile with the rows of other slots zeroed;
 //           tcgen05.mma.sp (A and metadata in TMEM, B in shared memory) then

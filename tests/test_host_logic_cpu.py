@@ -150,3 +150,24 @@ def test_tensor_parallel_cuts_pair_producer_and_consumer():
             pr = {name: (n, k) for name, n, k, _ in bench.projections(tp, rank)}
             assert pr["qkv_proj"][0] == 3 * pr["o_proj"][1]
             assert pr["gate_up_proj"][0] == 2 * pr["down_proj"][1]
+
+
+def test_convert_mapping_reports_the_runs_of_a_sorted_prefill_sized_batch():
+    """More than ops.FUSED_MAX_TOKENS rows in slot order: the run list the dequantise-once path
+    uses comes from the host's copy of the ids; smaller or unsorted batches get none."""
+    from deltazip_b200 import ops
+    from deltazip_b200.layers import DeltaMapping
+    from deltazip_b200.models import _convert_mapping
+    ids = [0] * 100 + [5] * 300 + [3] * 200          # slots: -1, 0, 1
+    out, (is_sorted, runs) = _convert_mapping(DeltaMapping(ids, [0, 5, 3]), [5, 3, None], 4, 1000, 0,
+                                              device="cpu")
+    assert len(ids) > ops.FUSED_MAX_TOKENS and is_sorted
+    assert runs == [(-1, 0, 100), (0, 100, 400), (1, 400, 600)]
+    assert out[0].tolist() == [-1] * 100 + [0] * 300 + [1] * 200
+    _, (is_sorted, runs) = _convert_mapping(DeltaMapping(ids[:200], [0, 5]), [5, 3, None], 4, 1000, 0,
+                                            device="cpu")
+    assert is_sorted and runs is None                 # decode-sized: the fused kernel serves it
+    mixed = [3] * 300 + [5] * 300
+    _, (is_sorted, runs) = _convert_mapping(DeltaMapping(mixed, [3, 5]), [5, 3, None], 4, 1000, 0,
+                                            device="cpu")
+    assert not is_sorted and runs is None
