@@ -82,7 +82,7 @@ def test_rotary_and_cache_write(qh, kvh):
     assert not kc[untouched].any() and not vc[untouched].any()
 
 
-@pytest.mark.parametrize("qh,kvh,splits", [(4, 4, 1), (8, 1, 1), (8, 2, 4), (32, 32, 1), (8, 1, 8)])
+@pytest.mark.parametrize("qh,kvh,splits", [(4, 4, 1), (8, 1, 1), (8, 2, 4), (32, 32, 1), (8, 1, 8), (8, 4, 2), (4, 2, 1)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_paged_decode_attention(qh, kvh, splits, dtype):
     from deltazip_b200 import ops
