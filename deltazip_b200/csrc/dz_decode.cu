@@ -202,10 +202,10 @@ rotary_cache_kernel(T* __restrict__ qkv, const int64_t* __restrict__ positions,
 // ---------------------------------------------------------------------------
 // Decode attention over the paged cache: one query token per sequence.
 // Grid (kv_heads, sequences, splits); a CTA handles the G = q_heads / kv_heads query heads that
-// share one kv head, over the key range of its split, so K and V are read once.  Warp w takes
-// tokens w, w + W, ...; a lane holds 4 of the 128 dims (one 8-byte load per token for K and for
-// V, 256 contiguous bytes per warp), scores are reduced with shuffles, softmax is computed
-// online per warp and the warps' partial (max, sum, acc) are merged through shared memory.
+// share one kv head, over the key range of its split, so K and V are read once.  The warps take
+// the rows of the range in turn (how the lanes share a row depends on G, see the two forms
+// below), scores are reduced with shuffles, softmax is computed online and the warps' partial
+// (max, sum, acc) are merged through shared memory.
 // With splits > 1 the CTA writes its partial triple to `partial` and the last CTA of a
 // (sequence, kv head) to arrive -- counted with an atomic ticket -- merges the splits; nothing
 // waits on anything.
@@ -323,57 +323,69 @@ paged_decode_attention_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
       }
     }
   } else {
-  float q[G][4];
+    // Grouped queries (4 or 8 query heads per kv head): lane -> (head g, part of the row), LPH =
+    // 32 / G lanes per head, each with 128 / LPH = 4 G dims of q and of the accumulator.  A warp
+    // takes one key/value row per step; the lanes of all heads read the same bytes of it (the
+    // loads coalesce into one row), a score needs log2(LPH) shuffles instead of five per head,
+    // and the K and V loads of a step are in flight together.
+    constexpr int LPH = 32 / G, DPL = 4 * G, NV = DPL / 8;     // NV 16-byte loads per row part
+    const int g = lane / LPH, part = lane % LPH;
+    float q[DPL], acc[DPL];
+    {
+      const T* qp = qkv + (size_t)seq * q_row_stride + (size_t)(kh * G + g) * kHeadDim + part * DPL;
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const uint2 v = *reinterpret_cast<const uint2*>(qkv + (size_t)seq * q_row_stride +
-                                                    (size_t)(kh * G + g) * kHeadDim + lane * 4);
-    const float2 a = Cvt<T>::up(v.x), b = Cvt<T>::up(v.y);
-    q[g][0] = a.x * scale; q[g][1] = a.y * scale; q[g][2] = b.x * scale; q[g][3] = b.y * scale;
-  }
-  float m[G], l[G], acc[G][4];
+      for (int v = 0; v < NV; ++v) {
+        const uint4 u = *reinterpret_cast<const uint4*>(qp + v * 8);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY; l[g] = 0.f;
-    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
-  }
-  // two tokens per iteration keep four 8-byte loads per lane in flight
-  for (int t = t0 + warp; t < t1; t += 2 * kWarps) {
-    const int tb = t + kWarps;
-    const bool two = tb < t1;
-    const size_t ra = ((size_t)table[t / block_size] * block_size + t % block_size) * kv_heads + kh;
-    const size_t rb = two ? ((size_t)table[tb / block_size] * block_size + tb % block_size) * kv_heads + kh : ra;
-    const uint2 ka = *reinterpret_cast<const uint2*>(k_cache + ra * kHeadDim + lane * 4);
-    const uint2 kb = *reinterpret_cast<const uint2*>(k_cache + rb * kHeadDim + lane * 4);
-    const uint2 va = *reinterpret_cast<const uint2*>(v_cache + ra * kHeadDim + lane * 4);
-    const uint2 vb = *reinterpret_cast<const uint2*>(v_cache + rb * kHeadDim + lane * 4);
-    const float2 ka0 = Cvt<T>::up(ka.x), ka1 = Cvt<T>::up(ka.y);
-    const float2 kb0 = Cvt<T>::up(kb.x), kb1 = Cvt<T>::up(kb.y);
-    const float2 va0 = Cvt<T>::up(va.x), va1 = Cvt<T>::up(va.y);
-    const float2 vb0 = Cvt<T>::up(vb.x), vb1 = Cvt<T>::up(vb.y);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float sa = q[g][0] * ka0.x + q[g][1] * ka0.y + q[g][2] * ka1.x + q[g][3] * ka1.y;
-      float sb = q[g][0] * kb0.x + q[g][1] * kb0.y + q[g][2] * kb1.x + q[g][3] * kb1.y;
-      sa = warp_sum(sa);
-      sb = two ? warp_sum(sb) : -INFINITY;
-      const float mn = fmaxf(m[g], fmaxf(sa, sb));
-      const float c = __expf(m[g] - mn), pa = __expf(sa - mn), pb = __expf(sb - mn);
-      l[g] = l[g] * c + pa + pb;
-      acc[g][0] = acc[g][0] * c + pa * va0.x + pb * vb0.x;
-      acc[g][1] = acc[g][1] * c + pa * va0.y + pb * vb0.y;
-      acc[g][2] = acc[g][2] * c + pa * va1.x + pb * vb1.x;
-      acc[g][3] = acc[g][3] * c + pa * va1.y + pb * vb1.y;
-      m[g] = mn;
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Cvt<T>::up(w[j]);
+          q[v * 8 + 2 * j] = f.x * scale;
+          q[v * 8 + 2 * j + 1] = f.y * scale;
+        }
+      }
     }
-  }
-  // merge the warps
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    for (int j = 0; j < DPL; ++j) acc[j] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    for (int t = t0 + warp; t < t1; t += kWarps) {
+      const size_t r = ((size_t)table[t / block_size] * block_size + t % block_size) * kv_heads + kh;
+      uint4 kk[NV], vv[NV];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s_acc[warp][g][lane * 4 + j] = acc[g][j];
-  }
+      for (int v = 0; v < NV; ++v) {
+        kk[v] = *reinterpret_cast<const uint4*>(k_cache + r * kHeadDim + part * DPL + v * 8);
+        vv[v] = *reinterpret_cast<const uint4*>(v_cache + r * kHeadDim + part * DPL + v * 8);
+      }
+      float sc = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const uint32_t w[4] = {kk[v].x, kk[v].y, kk[v].z, kk[v].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Cvt<T>::up(w[j]);
+          sc += q[v * 8 + 2 * j] * f.x + q[v * 8 + 2 * j + 1] * f.y;
+        }
+      }
+#pragma unroll
+      for (int o = LPH / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+      const float mn = fmaxf(m, sc);
+      const float c = __expf(m - mn), pw = __expf(sc - mn);
+      l = l * c + pw;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const uint32_t w[4] = {vv[v].x, vv[v].y, vv[v].z, vv[v].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Cvt<T>::up(w[j]);
+          acc[v * 8 + 2 * j] = acc[v * 8 + 2 * j] * c + pw * f.x;
+          acc[v * 8 + 2 * j + 1] = acc[v * 8 + 2 * j + 1] * c + pw * f.y;
+        }
+      }
+      m = mn;
+    }
+    if (part == 0) { s_m[warp][g] = m; s_l[warp][g] = l; }
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) s_acc[warp][g][part * DPL + j] = acc[j];
   }
   __syncthreads();
   // thread (g, d) pairs: G * 128 values, 256 threads
