@@ -262,7 +262,8 @@ int dz_grouped_gemm(const void* x, const void* base_matrix, const void* delta_ma
  *   (negative or slot_mapping == NULL: not cached).  Cache layout: [slots, kv_heads, 128] for K
  *   and for V.  head_dim must be 128.  serving/csrc/ops.h:49 + serving/csrc/cache.h:18.
  * dz_paged_attention_decode: one query token per sequence against its cached keys/values:
- *   out [num_seqs, q_heads * 128]; q is read from the fused rows (q_row_stride elements apart);
+ *   out [num_seqs, q_heads * 128]; q is read from the fused rows (q_row_stride elements apart, a
+ *   multiple of 8); q_heads / kv_heads must be 1, 2, 4 or 8;
  *   block_tables int32 [num_seqs, max_blocks]; seq_lens int32 [num_seqs] (cached tokens,
  *   the current one included).  splits > 1 divides every sequence's keys over that many CTAs
  *   (for few long sequences) and needs `workspace` of dz_paged_attention_workspace_bytes(),
