@@ -253,6 +253,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ __align__(8) uint64_t s_bars[2 * kMaxW + 2 * kMaxX + 2 * kMaxR + 2 * kMaxBuf + 2 + kNumWG];
   __shared__ WinS s_win[kMaxWin];
   __shared__ int s_slot[kTokenBlock];   // slot of each column of the token block (-1: base only)
+  __shared__ int s_tok[kTokenBlock];    // output row of each column (the table's permutation)
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_last, s_npre;
   __shared__ uint32_t s_fixpar[kNumWG];
@@ -307,30 +308,31 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // (barriers whose arrival counts do not depend on the batch, tensor memory, L2 prefetches of
   // the first W tiles).  Under programmatic dependent launch this runs while the predecessor's
   // last CTAs are still draining.
+  // Thread 0 needs only the W ring's "full" barriers to request the first W tiles, so it sets
+  // those up itself and, in the early-start form, issues the copies at once; the other barriers
+  // are initialised by one thread each meanwhile.
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kMaxW; ++i) {
-      mbar_init(smem_u32(&bar_w_full[i]), 1);
-      mbar_init(smem_u32(&bar_w_empty[i]), 1);
-    }
-    for (int i = 0; i < kMaxX; ++i) mbar_init(smem_u32(&bar_x_full[i]), 1);
-    for (int i = 0; i < kMaxR; ++i) {
-      mbar_init(smem_u32(&bar_r_full[i]), 1);
-      mbar_init(smem_u32(&bar_r_empty[i]), 128);
-    }
-    for (int i = 0; i < kMaxBuf; ++i) {
-      mbar_init(smem_u32(&bar_a_ready[i]), 128);
-      mbar_init(smem_u32(&bar_a_free[i]), 1);
-    }
-    mbar_init(smem_u32(bar_acc_empty), 128 * kNumWG);
-    for (int i = 0; i < kNumWG; ++i) {
-      mbar_init(smem_u32(&bar_fix[i]), 1);
-      s_fixpar[i] = 0;
-    }
+    for (int i = 0; i < kMaxW; ++i) mbar_init(smem_u32(&bar_w_full[i]), 1);
     s_abort = 0;
+    s_npre = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xc) : "memory");
+    if (p.stable && !p.delta_only) {
+      int issued = 0;
+      const int npre = min(p.w_stages, p.x_stages);
+      for (int u = u_begin; u < u_end && issued < npre; ++u) {
+        const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
+        const int nhalf = min(2, (p.K - k0) / kBlockK);
+        for (int h = 0; h < nhalf && issued < npre; ++h, ++issued) {
+          const uint32_t wfull = smem_u32(&bar_w_full[issued]);
+          mbar_expect_tx(wfull, kWTile);
+          tma_load_2d(s_wring + issued * kWTile, &map_w, k0 + h * kBlockK, n0, wfull);
+        }
+      }
+      s_npre = issued;
+    }
     // pull the first W tiles of this CTA's range towards L2 (a prefetch consumes no data, so it
     // is safe whatever the predecessor writes)
     int issued = 0;
@@ -343,6 +345,69 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                      : "memory");
     }
   }
+  {
+    // every other barrier whose arrival count does not depend on the batch: thread 32 + i takes
+    // barrier i of the array (x_empty and acc_full follow once the table has been read)
+    const int i = (int)threadIdx.x - 32;
+    constexpr int kBars = 2 * kMaxW + 2 * kMaxX + 2 * kMaxR + 2 * kMaxBuf + 2 + kNumWG;
+    if (i >= kMaxW && i < kBars) {
+      uint64_t* b = s_bars + i;
+      const bool later = (b >= bar_x_empty && b < bar_x_empty + kMaxX) || b == bar_acc_full;
+      uint32_t count = 1;
+      if ((b >= bar_r_empty && b < bar_r_empty + kMaxR) || (b >= bar_a_ready && b < bar_a_ready + kMaxBuf))
+        count = 128;
+      else if (b == bar_acc_empty)
+        count = 128 * kNumWG;
+      if (!later) {
+        mbar_init(smem_u32(b), count);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+      }
+    }
+    if (i >= 0 && i < kNumWG) s_fixpar[i] = 0;
+  }
+  // ---- the batch: windows and per-column slots of this token block ----
+  // The table's array offsets follow from (M, num_slots), which the call states; the header
+  // must agree.  All loads are independent of each other (one L2 round trip) and go to
+  // registers first: in the early-start form they are issued here, in front of the tensor
+  // memory allocation and the first barrier, so that their latency is hidden; the default form
+  // issues them behind the wait for the predecessor (the table may be its output).
+  const int* perm = nullptr;
+  const int* slot_of = nullptr;
+  const Window* wins = nullptr;
+  int t_hdr_m = 0, t_hdr_slots = 0, t_hdr_sorted = 0, t_win_end = 0, t_win_begin = 0;
+  int t_slot = -1, t_tok = p.row0 + (int)threadIdx.x;
+  int t_wslot = 0, t_wcol0 = 0, t_wncols = 0, t_wlo = 0, t_whi = 0;
+  auto load_table = [&]() {
+    if (!p.seg) return;
+    const SegHeader* hdr = reinterpret_cast<const SegHeader*>(p.seg);
+    const SegLayout lay = seg_layout(p.M, p.num_slots);
+    perm = reinterpret_cast<const int*>(p.seg + lay.perm);
+    slot_of = reinterpret_cast<const int*>(p.seg + lay.slot_of);
+    const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
+    wins = reinterpret_cast<const Window*>(p.seg + lay.windows);
+    t_hdr_m = hdr->capacity_M; t_hdr_slots = hdr->num_slots; t_hdr_sorted = hdr->sorted;
+    t_win_end = p.base_only ? 0 : bb[p.token_block + 1];
+    if (p.token_block == 0) {
+      // the windows of token block 0 start at entry 0; entries beyond the block's count are
+      // read (inside the table) but never used
+      const int cap = min(kMaxWin, seg_max_windows(p.M, p.num_slots));
+      if (!p.base_only && (int)threadIdx.x < cap) {
+        const Window* w = wins + threadIdx.x;
+        t_wslot = w->slot; t_wcol0 = w->col0; t_wncols = w->ncols; t_wlo = w->lo; t_whi = w->hi;
+      }
+    } else if (!p.base_only) {
+      t_win_begin = bb[p.token_block];
+    }
+    if ((int)threadIdx.x < kTokenBlock) {
+      const int prow = p.row0 + (int)threadIdx.x;
+      if (prow < p.M) {
+        if (!p.base_only) t_slot = slot_of[prow];
+        t_tok = perm[prow];
+      }
+    }
+  };
+  if (p.stable) load_table();
   if (warp == kWarpBase) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)),
@@ -371,23 +436,23 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (!p.stable) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    load_table();
   }
   if (INSTR && threadIdx.x == 0) tl[1] = globaltimer();
 
-  // The first W tiles (and, once the wait is behind, the first x tiles) are requested at once;
-  // the producer warp skips them later.
-  if (threadIdx.x == 0) {
+  // Default form: the first W and x tiles are requested here, right behind the wait; the
+  // producer warp skips them later.  (The early-start form requested its W tiles above and
+  // leaves x to the producer thread.)
+  if (threadIdx.x == 0 && !p.stable) {
     int issued = 0;
     const int npre = min(p.w_stages, p.x_stages);
     for (int u = u_begin; u < u_end && issued < npre; ++u) {
       const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
       const int nhalf = min(2, (p.K - k0) / kBlockK);
       for (int h = 0; h < nhalf && issued < npre; ++h, ++issued) {
-        if (!p.stable) {
-          const uint32_t xfull = smem_u32(&bar_x_full[issued]);
-          mbar_expect_tx(xfull, p.xb_bytes);
-          tma_load_2d(s_xring + issued * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
-        }
+        const uint32_t xfull = smem_u32(&bar_x_full[issued]);
+        mbar_expect_tx(xfull, p.xb_bytes);
+        tma_load_2d(s_xring + issued * p.xb_bytes, &map_xc, k0 + h * kBlockK, p.row0, xfull);
         if (!p.delta_only) {
           const uint32_t wfull = smem_u32(&bar_w_full[issued]);
           mbar_expect_tx(wfull, kWTile);
@@ -398,44 +463,25 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     s_npre = issued;
   }
 
-  // ---- the batch: windows and per-column slots of this token block ----
-  // The table's array offsets follow from (M, num_slots), which the call states; the header
-  // must agree.  All reads below are independent of each other (one L2 round trip): the
-  // windows of token block 0 start at entry 0, and entries beyond the block's count are read
-  // (inside the table) but never used.
+  // ---- the table's entries go to shared memory ----
   int nwin = 0;
   bool bad = false;
-  const int* perm = nullptr;
-  const int* slot_of = nullptr;
   if (p.seg) {
-    const SegHeader* hdr = reinterpret_cast<const SegHeader*>(p.seg);
-    const SegLayout lay = seg_layout(p.M, p.num_slots);
-    perm = reinterpret_cast<const int*>(p.seg + lay.perm);
-    slot_of = reinterpret_cast<const int*>(p.seg + lay.slot_of);
-    const int* bb = reinterpret_cast<const int*>(p.seg + lay.block_begin);
-    const Window* wins = reinterpret_cast<const Window*>(p.seg + lay.windows);
-    const int hdr_m = hdr->capacity_M, hdr_slots = hdr->num_slots, hdr_sorted = hdr->sorted;
-    const int win_end = p.base_only ? 0 : bb[p.token_block + 1];
-    int win_begin = 0;
+    bad = (t_hdr_m != p.M) || (t_hdr_slots != p.num_slots) || (p.tokens_sorted && !t_hdr_sorted);
+    if (!p.base_only && !bad) nwin = min(t_win_end - t_win_begin, kMaxWin);
     if (p.token_block == 0) {
       const int cap = min(kMaxWin, seg_max_windows(p.M, p.num_slots));
       if (!p.base_only && (int)threadIdx.x < cap) {
-        const Window w = wins[threadIdx.x];
         WinS ws;
-        ws.slot = w.slot;
-        ws.col0 = w.col0 - p.row0;
-        ws.ncols = w.ncols;
-        ws.lohi = (w.lo - w.col0) | ((w.hi - w.col0) << 16);
+        ws.slot = t_wslot;
+        ws.col0 = t_wcol0 - p.row0;
+        ws.ncols = t_wncols;
+        ws.lohi = (t_wlo - t_wcol0) | ((t_whi - t_wcol0) << 16);
         s_win[threadIdx.x] = ws;
       }
-    } else if (!p.base_only) {
-      win_begin = bb[p.token_block];
-    }
-    bad = (hdr_m != p.M) || (hdr_slots != p.num_slots) || (p.tokens_sorted && !hdr_sorted);
-    if (!p.base_only && !bad) nwin = min(win_end - win_begin, kMaxWin);
-    if (p.token_block != 0) {
+    } else {
       for (int i = threadIdx.x; i < nwin; i += kThreads) {
-        const Window w = wins[win_begin + i];
+        const Window w = wins[t_win_begin + i];
         WinS ws;
         ws.slot = w.slot;
         ws.col0 = w.col0 - p.row0;
@@ -445,9 +491,9 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   }
-  for (int i = threadIdx.x; i < kTokenBlock; i += kThreads) {
-    const int prow = p.row0 + i;
-    s_slot[i] = (slot_of && !p.base_only && prow < p.M) ? slot_of[prow] : -1;
+  if ((int)threadIdx.x < kTokenBlock) {
+    s_slot[threadIdx.x] = t_slot;
+    s_tok[threadIdx.x] = t_tok;
   }
   if (threadIdx.x == 0) {
     // freed by the base issuer's commit and, when there are windows, by every thread of every
@@ -939,7 +985,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int i = 0; i < 8; ++i) {
               const int prow = p.row0 + col + i;
               if (prow < p.M) {
-                const int tok = perm ? perm[prow] : prow;
+                const int tok = s_tok[col + i];   // read in the prologue: no L2 round trip here
                 const size_t at = (size_t)tok * (size_t)p.ldy + n0 + r;
                 if (p.push_world == 0) {
                   store_out<DT>(p.y, at, __uint_as_float(v[i]), p.accumulate);
