@@ -175,7 +175,7 @@ def allreduce_selfcheck(car, rank, world, device):
         return acc.to(x.dtype)
 
     # every rank runs every call whatever it finds (the calls are collective); the first
-    # difference is kept and the verdict is agreed on at the end
+    # difference is kept and the outcome is agreed on at the end
     bad = None
     g = torch.Generator(device=device).manual_seed(100 + rank)
     for variant in (1, 2):                   # the one-shot and the two-stage kernel, forced in turn
