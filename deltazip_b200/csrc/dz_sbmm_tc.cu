@@ -245,7 +245,25 @@ struct WinS {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int BITS, int DT>
+// Per-mode constants.  WIDE = token block of more than 64 columns: three classes and a 128-column
+// accumulator pair; otherwise four classes and 64 columns.  The packed-stage ring depth follows
+// from the shared-memory budget at the mode's widest block.
+__host__ __device__ constexpr int mode_classes(bool wide) { return wide ? 3 : 4; }
+__host__ __device__ constexpr int mode_dcols(bool wide) { return wide ? 128 : 64; }
+__host__ __device__ constexpr int mode_w_stages(bool wide) { return wide ? DZ_W_STAGES_WIDE : 3; }
+__host__ __device__ constexpr int mode_x_stages(bool wide) { return wide ? DZ_X_STAGES_WIDE : 4; }
+__host__ __device__ constexpr int mode_r_per_class(int bits, bool wide) {
+  const int fixed = mode_x_stages(wide) * mode_dcols(wide) * 128 + mode_w_stages(wide) * kWTile +
+                    2 * kNumWG * kWinBytes;
+  const int r = (kSmemBudget - fixed) / (mode_classes(wide) * rstage_bytes(bits));
+  return r < DZ_MAX_R_PER_CLASS ? r : DZ_MAX_R_PER_CLASS;
+}
+static_assert(mode_r_per_class(4, false) >= 2 && mode_r_per_class(4, true) >= 2, "ring too shallow");
+static_assert(mode_classes(false) * mode_r_per_class(2, false) <= kMaxR, "ring barriers");
+
+// FULLK: K is a multiple of the 128-wide k-unit, so every unit has both half-tiles (the common
+// case; the tests on one half-tile in the loops fold away).
+template <int BITS, int DT, bool FULLK, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1)
 sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xc,
                const Params p) {
@@ -271,15 +289,18 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int C = p.nclass;
+  constexpr int C = mode_classes(WIDE);
+  constexpr int kDcols = mode_dcols(WIDE);
+  constexpr int kWStages = mode_w_stages(WIDE), kXStages = mode_x_stages(WIDE);
+  constexpr int kRPer = mode_r_per_class(BITS, WIDE);
   const int nbuf = 2 * C;
 
   // ---- shared memory carve-up (1024-byte aligned regions) ----
   const uint32_t dyn0 = smem_u32(smem_dyn);
   const uint32_t sbase = (dyn0 + 1023u) & ~1023u;
   const uint32_t s_wring = sbase;
-  const uint32_t off_x = p.w_stages * kWTile;
-  const uint32_t off_win = off_x + p.x_stages * p.xb_bytes;
+  const uint32_t off_x = kWStages * kWTile;
+  const uint32_t off_win = off_x + kXStages * p.xb_bytes;
   const uint32_t off_r = off_win + 2 * kNumWG * kWinBytes;   // every warpgroup owns two
   const uint32_t s_xring = sbase + off_x;
   const uint32_t s_winbuf = sbase + off_win;
@@ -321,10 +342,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xc) : "memory");
     if (p.stable && !p.delta_only) {
       int issued = 0;
-      const int npre = min(p.w_stages, p.x_stages);
+      const int npre = min(kWStages, kXStages);
       for (int u = u_begin; u < u_end && issued < npre; ++u) {
         const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
-        const int nhalf = min(2, (p.K - k0) / kBlockK);
+        const int nhalf = FULLK ? 2 : min(2, (p.K - k0) / kBlockK);
         for (int h = 0; h < nhalf && issued < npre; ++h, ++issued) {
           const uint32_t wfull = smem_u32(&bar_w_full[issued]);
           mbar_expect_tx(wfull, kWTile);
@@ -338,7 +359,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int issued = 0;
     for (int u = u_begin; u < u_end && issued < kPrefetchTiles && !p.delta_only; ++u) {
       const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
-      const int nhalf = min(2, (p.K - k0) / kBlockK);
+      const int nhalf = FULLK ? 2 : min(2, (p.K - k0) / kBlockK);
       for (int h = 0; h < nhalf; ++h, ++issued)
         asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&map_w),
                      "r"(k0 + h * kBlockK), "r"(n0)
@@ -445,10 +466,10 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // leaves x to the producer thread.)
   if (threadIdx.x == 0 && !p.stable) {
     int issued = 0;
-    const int npre = min(p.w_stages, p.x_stages);
+    const int npre = min(kWStages, kXStages);
     for (int u = u_begin; u < u_end && issued < npre; ++u) {
       const int n0 = (u / KU) * kTileN, k0 = (u % KU) * kUnitK;
-      const int nhalf = min(2, (p.K - k0) / kBlockK);
+      const int nhalf = FULLK ? 2 : min(2, (p.K - k0) / kBlockK);
       for (int h = 0; h < nhalf && issued < npre; ++h, ++issued) {
         const uint32_t xfull = smem_u32(&bar_x_full[issued]);
         mbar_expect_tx(xfull, p.xb_bytes);
@@ -508,7 +529,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (warp >= kFirstWGWarp && nwin > 0) {
     const int wg = (warp - kFirstWGWarp) >> 2;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    for (int c = wg; c < p.cols / 16; c += kNumWG) tmem_st16_zero(lane_addr + p.dcols + c * 16);
+    for (int c = wg; c < p.cols / 16; c += kNumWG) tmem_st16_zero(lane_addr + kDcols + c * 16);
     tmem_wait_st();
   }
   tc_fence_before();
@@ -523,7 +544,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
   const int npre_w = s_npre;                     // W half-tiles requested in the prologue
   const int npre_x = p.stable ? 0 : s_npre;      // x half-tiles requested in the prologue
-  const uint32_t a_col0 = 2 * p.dcols;          // TMEM column of expanded-A buffer 0
+  const uint32_t a_col0 = 2 * kDcols;          // TMEM column of expanded-A buffer 0
   const uint32_t e_col0 = a_col0 + nbuf * 32;   // TMEM column of metadata buffer 0
 
   if (bad) {
@@ -542,7 +563,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
       }
-      Ring rw(p.w_stages, 1), rx(p.x_stages, 1);
+      Ring rw(kWStages, 1), rx(kXStages, 1);
       int cnt = 0;   // half-tiles so far; the first ones were requested in the prologue
       for (int u = u_begin; u < u_end;) {
         const int tile = u / KU, ku0 = u % KU;
@@ -550,7 +571,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int n0 = tile * kTileN;
         for (int ku = ku0; ku < ku1; ++ku) {
           const int k0 = ku * kUnitK;
-          const int nhalf = min(2, (p.K - k0) / kBlockK);
+          const int nhalf = FULLK ? 2 : min(2, (p.K - k0) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
             if (cnt >= npre_x) {
               mbar_wait(smem_u32(&bar_x_empty[rx.idx]), rx.par, abort_flag, p.status);
@@ -588,13 +609,13 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int tile = u / KU, ku0 = u % KU;
         const int ku1 = min(KU, ku0 + (u_end - u));
         for (int ku = ku0; ku < ku1; ++ku) {
-          const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
+          const int nhalf = FULLK ? 2 : min(2, (p.K - ku * kUnitK) / kBlockK);
           const uint32_t code_bytes = nhalf * codes_block_bytes(BITS);
           const uint32_t meta_bytes = nhalf * kMetaBlockBytes;
           const size_t blk = (size_t)tile * p.num_kblocks + (size_t)ku * 2;
           for (int j = 0; j < cnt_max; ++j) {
             if (j < cnt_t) {
-              const int slot_idx = t * p.r_per_class + rs;
+              const int slot_idx = t * kRPer + rs;
               const int slot = s_win[t + j * C].slot;
               mbar_wait(smem_u32(&bar_r_empty[slot_idx]), par, abort_flag, p.status);
               const uint32_t full = smem_u32(&bar_r_full[slot_idx]);
@@ -604,7 +625,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         code_bytes, full);
               bulk_load(dst + raw_bytes(BITS),
                         p.meta + (size_t)slot * p.mstride + blk * kMetaBlockBytes, meta_bytes, full);
-              if (++rs == p.r_per_class) { rs = 0; par ^= 1; }
+              if (++rs == kRPer) { rs = 0; par ^= 1; }
             }
           }
         }
@@ -614,7 +635,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else if (warp == kWarpBase) {
     // =========================== base MMA issuer ===========================
     if (lane == 0) {
-      Ring rw(p.w_stages, 0), rx(p.x_stages, 0);
+      Ring rw(kWStages, 0), rx(kXStages, 0);
       int pacc = 1;
       const uint32_t idesc_base = make_idesc<DT>(p.cols, false);
       for (int u = u_begin; u < u_end;) {
@@ -625,7 +646,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         uint32_t acc = 0;
         for (int ku = ku0; ku < ku1; ++ku) {
-          const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
+          const int nhalf = FULLK ? 2 : min(2, (p.K - ku * kUnitK) / kBlockK);
           for (int h = 0; h < nhalf; ++h) {
             mbar_wait(smem_u32(&bar_x_full[rx.idx]), rx.par, abort_flag, p.status);
             if (!p.delta_only) {
@@ -671,7 +692,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         pacc ^= 1;
         tc_fence_after();
         for (int ku = ku0; ku < ku1; ++ku) {
-          const int nhalf = min(2, (p.K - ku * kUnitK) / kBlockK);
+          const int nhalf = FULLK ? 2 : min(2, (p.K - ku * kUnitK) / kBlockK);
           for (int j = 0; j < cnt_t; ++j, ++n) {
             if (par >= 0 && (n & 1) != par) continue;
             const WinS ws = s_win[t + j * C];
@@ -682,7 +703,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tc_fence_after();
             const uint32_t win_lo = desc_lo(s_winbuf + buf * kWinBytes);
             const uint32_t idesc = make_idesc<DT>(ws.ncols, true);
-            const uint32_t dcol = tmem_base + p.dcols + ws.col0;
+            const uint32_t dcol = tmem_base + kDcols + ws.col0;
             const uint32_t acol = tmem_base + a_col0 + buf * 32;
             const uint32_t ecol = tmem_base + e_col0 + buf * 4;
             umma_ts_sp_x2(dcol, acol, win_lo, ecol, idesc);
@@ -706,7 +727,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const bool active = (wg < C) && nwin > 0;
     const int cnt_t = active ? (nwin - wg + C - 1) / C : 0;
-    Ring rx(p.x_stages, 0);
+    Ring rx(kXStages, 0);
     int pacc = 0, n = 0, rs = 0;
     uint32_t rpar = 0;
     bool cta_first_fragment = true;
@@ -719,7 +740,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int n0 = tile * kTileN;
       for (int ku = ku0; ku < ku1 && active; ++ku) {
         const int k0 = ku * kUnitK;
-        const int nhalf = min(2, (p.K - k0) / kBlockK);
+        const int nhalf = FULLK ? 2 : min(2, (p.K - k0) / kBlockK);
         // the unit's x half-tiles
         uint32_t xsrc0 = 0, xsrc1 = 0;
         int xslot0 = 0, xslot1 = 0;
@@ -733,11 +754,11 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int j = 0; j < cnt_t; ++j, ++n) {
           const WinS ws = s_win[wg + j * C];
           const int buf = wg + C * (n & 1);
-          const int rslot = wg * p.r_per_class + rs;
+          const int rslot = wg * kRPer + rs;
           if (acc_on) { const long long t2 = clock64(); if (j == 0) a_x += t2 - tq; tq = t2; }
           mbar_wait(smem_u32(&bar_r_full[rslot]), rpar, abort_flag, p.status);
           if (acc_on) { const long long t2 = clock64(); a_r += t2 - tq; tq = t2; }
-          if (++rs == p.r_per_class) { rs = 0; rpar ^= 1; }
+          if (++rs == kRPer) { rs = 0; rpar ^= 1; }
           mbar_wait(smem_u32(&bar_a_free[buf]), ((n >> 1) & 1) ^ 1, abort_flag, p.status);
           if (acc_on) { const long long t2 = clock64(); a_free += t2 - tq; tq = t2; }
           tc_fence_after();
@@ -908,7 +929,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           } else {
             tmem_ld8(lane_addr + col, v);
           }
-          if (nwin > 0) tmem_ld8(lane_addr + p.dcols + col, d);
+          if (nwin > 0) tmem_ld8(lane_addr + kDcols + col, d);
           tmem_wait_ld();
           if (nwin > 0) {
 #pragma unroll
@@ -1001,7 +1022,7 @@ sbmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               __stcg(p.partials + (my_park + (uint32_t)((col + i) * 128 + r)), __uint_as_float(v[i]));
           }
         }
-        if (nwin > 0) tmem_st16_zero(lane_addr + p.dcols + c * 16);   // D_delta restarts from zero
+        if (nwin > 0) tmem_st16_zero(lane_addr + kDcols + c * 16);   // D_delta restarts from zero
       }
       tmem_wait_st();
       tc_fence_before();
@@ -1077,7 +1098,7 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const uint8_t* _
 // ---------------------------------------------------------------------------
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[4] = {false, false, false, false};
+  bool attr_set[16] = {};
 };
 DeviceInfo& device_info(int dev) {
   static DeviceInfo info[64];
@@ -1165,7 +1186,6 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
   p.counters = reinterpret_cast<int*>(ws + kWsCounters);
   p.partials = reinterpret_cast<float*>(ws + kWsPartials);
 
-  const int kidx = ((a.bits == 2) ? 0 : 1) + (dt ? 2 : 0);
   const int num_tb = (a.M + kTokenBlock - 1) / kTokenBlock;
   for (int tb = 0; tb < num_tb; ++tb) {
     p.token_block = tb;
@@ -1178,13 +1198,24 @@ int launch_sbmm(const dz_sbmm_args& a, bool base_only, cudaStream_t st) {
     p.w_stages = p.cols <= 64 ? 3 : DZ_W_STAGES_WIDE;
     const int fixed = p.x_stages * p.xb_bytes + p.w_stages * kWTile + 2 * kNumWG * kWinBytes;
     const int rstage = rstage_bytes(a.bits);
-    p.r_per_class = min(DZ_MAX_R_PER_CLASS, (kSmemBudget - fixed) / (p.nclass * rstage));
-    if (p.r_per_class < 2 || p.nclass * p.r_per_class > kMaxR) return DZ_ERR_UNSUPPORTED;
+    const bool wide = p.cols > 64;
+    p.r_per_class = mode_r_per_class(a.bits, wide);
     rc = make_map(&map_xc, xsrc, a.M, a.K, p.cols, dt);
     if (rc) return rc;
     const size_t smem = (size_t)fixed + (size_t)p.nclass * p.r_per_class * rstage + 1024;
-    auto kern = dt ? ((a.bits == 2) ? sbmm_tc_kernel<2, 1> : sbmm_tc_kernel<4, 1>)
-                   : ((a.bits == 2) ? sbmm_tc_kernel<2, 0> : sbmm_tc_kernel<4, 0>);
+    const bool fullk = (a.K % kUnitK) == 0;
+    using Kern = void (*)(const CUtensorMap, const CUtensorMap, const Params);
+    static const Kern kerns[16] = {
+        sbmm_tc_kernel<2, 0, false, false>, sbmm_tc_kernel<4, 0, false, false>,
+        sbmm_tc_kernel<2, 1, false, false>, sbmm_tc_kernel<4, 1, false, false>,
+        sbmm_tc_kernel<2, 0, true, false>,  sbmm_tc_kernel<4, 0, true, false>,
+        sbmm_tc_kernel<2, 1, true, false>,  sbmm_tc_kernel<4, 1, true, false>,
+        sbmm_tc_kernel<2, 0, false, true>,  sbmm_tc_kernel<4, 0, false, true>,
+        sbmm_tc_kernel<2, 1, false, true>,  sbmm_tc_kernel<4, 1, false, true>,
+        sbmm_tc_kernel<2, 0, true, true>,   sbmm_tc_kernel<4, 0, true, true>,
+        sbmm_tc_kernel<2, 1, true, true>,   sbmm_tc_kernel<4, 1, true, true>};
+    const int kidx = ((a.bits == 2) ? 0 : 1) + (dt ? 2 : 0) + (fullk ? 4 : 0) + (wide ? 8 : 0);
+    Kern kern = kerns[kidx];
     if (!di.attr_set[kidx]) {
       DZ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
       di.attr_set[kidx] = true;
