@@ -503,7 +503,7 @@ def run_ours(args):
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches,
             "roofline": {
-                "bound": "hbm", "kernel": "sbmm_tc_kernel<4,0>",
+                "bound": "hbm", "kernel": "sbmm_tc_kernel<4,0,FULLK,false> (4-bit, fp16, 64-column token block)",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": step_bytes / n_calls,
@@ -971,7 +971,7 @@ def run_decode(args):
                     "ms_per_step": e2e_ms / steps},
             "gpu_launches": launches_per_step * steps,
             "roofline": {
-                "bound": "hbm", "kernel": "sbmm_tc_kernel<%d,0>" % bits,
+                "bound": "hbm", "kernel": "sbmm_tc_kernel<%d,0,FULLK,%s>" % (bits, "true" if b > 64 else "false"),
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": step_bytes / n_calls,
